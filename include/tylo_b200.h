@@ -1,0 +1,233 @@
+/* libtylo_b200 — C ABI of the B200 (sm_100a) implementation of Tylo's transformer hot path.
+ *
+ * Each entry point replaces one launch group of the Tylo.jl package: the place where a
+ * host wrapper such as `attention!` hands its arrays to `@cutile(blocks=…, kernel(…))`
+ * (src/Tylo.jl:10-12).  The citation beside each declaration names the wrapper (and the
+ * kernels it launches) that the entry point stands in for; paths are relative to the
+ * Tylo.jl project root.
+ *
+ * Conventions
+ *  - Arrays are dense, column-major (Julia) device buffers passed as raw pointers with
+ *    explicit extents.  A Julia array of size (D, S, H, B) is the same memory as a
+ *    C-contiguous array indexed [b][h][s][d].
+ *  - Every buffer is owned by the caller.  Except where a declaration says otherwise the
+ *    library allocates no device memory, never synchronises, and enqueues all work on
+ *    the `stream` argument (a `cudaStream_t`; NULL = the legacy default stream).
+ *  - Optional arrays are nullable pointers.
+ *  - Every function returns a `tylo_status`; `tylo_b200_last_error()` gives the
+ *    thread-local message of the last non-zero status.  Arguments are validated before
+ *    anything is enqueued, so a non-zero status means no work was launched.
+ *  - Data pointers must be 16-byte aligned (true of any CUDA allocation).
+ */
+#ifndef TYLO_B200_H
+#define TYLO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TYLO_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum {
+  TYLO_OK = 0,
+  TYLO_ERR_INVALID_ARGUMENT = 1, /* null / non-positive extent / inconsistent shapes (the wrappers' @assert) */
+  TYLO_ERR_UNSUPPORTED = 2,      /* valid request this library has no kernel for (there is no fallback) */
+  TYLO_ERR_MISALIGNED = 3,       /* a data pointer is not 16-byte aligned */
+  TYLO_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed; message holds its text */
+  TYLO_ERR_NCCL = 5,             /* an NCCL call failed */
+  TYLO_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait gave up (see tylo_b200_device_status) */
+  TYLO_ERR_WORKSPACE = 7         /* caller-provided workspace is too small */
+} tylo_status;
+
+typedef enum { TYLO_F32 = 0, TYLO_BF16 = 1, TYLO_F16 = 2 } tylo_dtype;
+
+typedef void* tylo_stream_t; /* cudaStream_t */
+
+int32_t tylo_b200_version(void);
+const char* tylo_b200_status_string(int32_t status);
+const char* tylo_b200_last_error(void);
+
+/* ---- mod descriptors (src/attention/mods.jl) -------------------------------------------------
+ * The Julia wrapper maps mod *types* to these plain structs by dispatch.  All enabled mask
+ * terms are AND-ed (AndMask, mods.jl:151-157).  Positions are 0-based and absolute: query
+ * position = row index + input_pos (flex.jl:41), key position = row index. */
+#define TYLO_MASK_CAUSAL 1u    /* CausalMask: q >= kv (mods.jl:109-110) */
+#define TYLO_MASK_SLIDING 2u   /* SlidingWindowMask(w): q >= kv && q <= kv + w (mods.jl:116-120) */
+#define TYLO_MASK_DOCUMENT 4u  /* DocumentMask: doc_q[q] == doc_kv[kv] (mods.jl:141-147) */
+#define TYLO_MASK_PREFIX 8u    /* PrefixMask(len): kv < len (mods.jl:127-131) */
+#define TYLO_MASK_PREFIX_LM 16u /* prefix_lm(len) = causal | prefix (mods.jl:178) as one AND term */
+
+typedef struct {
+  uint32_t flags;
+  int32_t window;             /* SLIDING */
+  int32_t prefix_len;         /* PREFIX / PREFIX_LM */
+  int32_t reserved;
+  const int32_t* doc_q;       /* DOCUMENT: device int32 ids indexed by absolute query position */
+  const int32_t* doc_kv;      /* DOCUMENT: device int32 ids indexed by key position */
+  int64_t doc_batch_stride;   /* 0: one table shared by every batch (the reference's semantics);
+                                 otherwise element stride between per-batch tables */
+  int64_t doc_q_len;          /* number of ids per table (bounds: input_pos + Sq <= doc_q_len) */
+  int64_t doc_kv_len;
+} tylo_mask_desc;
+
+#define TYLO_SCORE_ALIBI 1u         /* AliBiScore: s + slopes[h] * (q - kv), one slope per query head (mods.jl:205-209) */
+#define TYLO_SCORE_SOFTCAP 2u       /* SoftCapScore: cap * tanh(s / cap) (mods.jl:194-198) */
+#define TYLO_SCORE_SOFTCAP_FIRST 4u /* with both set: 0 = softcap ∘ alibi (alibi first), 1 = alibi ∘ softcap (mods.jl:244-249) */
+
+typedef struct {
+  uint32_t flags;
+  float cap;
+  const float* slopes; /* device fp32, length H */
+  float* d_slopes;     /* backward only, nullable: accumulates the slope gradient atomically
+                          (grad_shadow semantics, mods.jl:296-303); caller zeroes it */
+} tylo_score_desc;
+
+/* ---- fused attention ---------------------------------------------------------------------------
+ * attention! → mha_fwd (src/attention/attention.jl:219-262, kernel :6-88).
+ * Q (Dk,Sq,H,B)  K (Dk,Sk,Hkv,B)  V (Dv,Sk,Hkv,B)  O (Dv,Sq,H,B);  scale = 1/sqrt(Dk).
+ * M, L: optional fp32 (Sq,H,B) checkpoints: M = row max of s*scale*log2(e), L = sum exp2(.-M).
+ * k_lengths / q_lengths: optional device int32 (B,) valid lengths (attention.jl:25-26,37-46,60).
+ * causal masks kv > q + input_pos.  dtype: storage type of Q,K,V,O.  fp32 storage is computed
+ * in true fp32 (the reference's default rounds operands to TF32). */
+int32_t tylo_b200_attention_fwd(void* O, const void* Q, const void* K, const void* V,
+                                float* M, float* L,
+                                const int32_t* k_lengths, const int32_t* q_lengths,
+                                int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                int32_t H, int32_t Hkv, int32_t B,
+                                int32_t input_pos, int32_t causal, int32_t dtype,
+                                tylo_stream_t stream);
+
+/* Bytes of caller-provided workspace the backward needs for these extents (0 is possible). */
+int64_t tylo_b200_attention_bwd_workspace_bytes(int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                                int32_t H, int32_t Hkv, int32_t B, int32_t dtype);
+
+/* ∇attention! → mha_bwd_preprocess + fill! + mha_bwd (attention.jl:297-357, kernels :90-198).
+ * Overwrites dQ, dK, dV (no pre-zeroing needed).  Delta is the fp32 (Sq,H,B) scratch `Δ`;
+ * dO_scaled is the reference's scratch `Ō′` (same shape/type as O): accepted for API
+ * compatibility, may be NULL, not required to hold anything afterwards. */
+int32_t tylo_b200_attention_bwd(void* dQ, void* dK, void* dV,
+                                const void* Q, const void* K, const void* V,
+                                const void* O, const void* dO,
+                                const float* M, const float* L,
+                                void* dO_scaled, float* Delta,
+                                void* workspace, int64_t workspace_bytes,
+                                const int32_t* k_lengths, const int32_t* q_lengths,
+                                int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                int32_t H, int32_t Hkv, int32_t B,
+                                int32_t input_pos, int32_t causal, int32_t dtype,
+                                tylo_stream_t stream);
+
+/* flex_attention! → flex_fwd (src/attention/flex.jl:312-383, kernel :22-105).
+ * As attention_fwd plus score/mask mods; natural-base statistics: M = row max of the modded
+ * score, L = sum exp(.-M); a fully masked query gives O = 0, M = -Inf, L = 0 (flex.jl:86-102).
+ * qk_scale <= 0 selects the default 1/sqrt(Dk) (flex.jl:337).  mask/score may be NULL
+ * (FullMask / NoOpScore).  block_sparse only permits skipping provably empty tiles. */
+int32_t tylo_b200_flex_attention_fwd(void* O, const void* Q, const void* K, const void* V,
+                                     float* M, float* L,
+                                     const tylo_mask_desc* mask, const tylo_score_desc* score,
+                                     int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                     int32_t H, int32_t Hkv, int32_t B,
+                                     int32_t input_pos, float qk_scale, int32_t block_sparse,
+                                     int32_t dtype, tylo_stream_t stream);
+
+/* ∇flex_attention! → mha_bwd_preprocess + fill! + flex_bwd (flex.jl:445-511, kernel :197-289;
+ * score VJPs mods.jl:288-319). */
+int32_t tylo_b200_flex_attention_bwd(void* dQ, void* dK, void* dV,
+                                     const void* Q, const void* K, const void* V,
+                                     const void* O, const void* dO,
+                                     const float* M, const float* L,
+                                     void* dO_scaled, float* Delta,
+                                     void* workspace, int64_t workspace_bytes,
+                                     const tylo_mask_desc* mask, const tylo_score_desc* score,
+                                     int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                     int32_t H, int32_t Hkv, int32_t B,
+                                     int32_t input_pos, float qk_scale, int32_t block_sparse,
+                                     int32_t dtype, tylo_stream_t stream);
+
+/* ---- split-KV decode ---------------------------------------------------------------------------
+ * decode_attention! → mha_decode_split_fwd + mha_decode_combine
+ * (src/attention/decode.jl:158-212, kernels :28-143).
+ * Q (Dk,H,B)  K (Dk,Sk,Hkv,B)  V (Dv,Sk,Hkv,B)  O (Dv,H,B)  lengths device int32 (B,).
+ * Scratch (decode.jl:223-231): O_partial fp32 (Dv,H,B,n_splits) — normalised per split —,
+ * M_partial (log2 units) and L_partial fp32 (H,B,n_splits).  Split s owns keys
+ * [s*split_size, min((s+1)*split_size, len)), split_size = ceil(ceil(Sk/n_splits)/64)*64
+ * (decode.jl:183, TILE_N = 64); an empty split writes (0, -Inf, 0). */
+int32_t tylo_b200_decode_attention(void* O, const void* Q, const void* K, const void* V,
+                                   const int32_t* lengths,
+                                   float* O_partial, float* M_partial, float* L_partial,
+                                   int32_t n_splits,
+                                   int32_t Dk, int32_t Dv, int32_t Sk,
+                                   int32_t H, int32_t Hkv, int32_t B,
+                                   int32_t dtype, tylo_stream_t stream);
+
+/* First half only (mha_decode_split_fwd, decode.jl:187-199): fills the partials. */
+int32_t tylo_b200_decode_split(const void* Q, const void* K, const void* V,
+                               const int32_t* lengths,
+                               float* O_partial, float* M_partial, float* L_partial,
+                               int32_t n_splits,
+                               int32_t Dk, int32_t Dv, int32_t Sk,
+                               int32_t H, int32_t Hkv, int32_t B,
+                               int32_t dtype, tylo_stream_t stream);
+
+/* Second half (mha_decode_combine, decode.jl:201-209, algebra :119-140).  `o_stride` and
+ * `ml_stride` are the element strides between consecutive splits in O_partial and in
+ * M_partial/L_partial (H*B*Dv and H*B for the scratch above); other strides let the same
+ * routine merge per-GPU partials gathered into one buffer.  If O is non-NULL the merged
+ * result is stored there in `dtype`.  If O_merged/M_merged/L_merged are non-NULL the merged
+ * partial (normalised fp32 O, max, sum) is stored as well, for a further merge level. */
+int32_t tylo_b200_decode_combine(void* O, float* O_merged, float* M_merged, float* L_merged,
+                                 const float* O_partial, const float* M_partial,
+                                 const float* L_partial,
+                                 int32_t n_splits, int64_t o_stride, int64_t ml_stride,
+                                 int32_t Dv, int32_t H, int32_t B,
+                                 int32_t dtype, tylo_stream_t stream);
+
+/* A split count that fills the GPU for these extents (the reference's default of 8 gives only
+ * 8*Hkv*B blocks, decode.jl:163,187). */
+int32_t tylo_b200_decode_suggest_splits(int32_t Sk, int32_t Hkv, int32_t B);
+
+/* ---- softmax -----------------------------------------------------------------------------------
+ * softmax! → softmax_fwd / softmax_fwd_single (src/softmax/softmax.jl:96-105, kernels :6-33,:62-72).
+ * X, Y (M,N): softmax along dim 1 (the contiguous one), one column per n. */
+int32_t tylo_b200_softmax_fwd(void* Y, const void* X, int64_t M, int64_t N, int32_t dtype,
+                              tylo_stream_t stream);
+/* ∇softmax! → softmax_bwd / softmax_bwd_single (softmax.jl:127-136, kernels :35-60,:74-85):
+ * dX = Y ∘ (dY − Σ Y∘dY). */
+int32_t tylo_b200_softmax_bwd(void* dX, const void* dY, const void* Y, int64_t M, int64_t N,
+                              int32_t dtype, tylo_stream_t stream);
+
+/* ---- RMSNorm -----------------------------------------------------------------------------------
+ * rms_norm! → rms_norm_fwd (src/norm/rms_norm.jl:115-128, kernel :6-32).
+ * X, Y (M,N), W (M,), optional Rstd fp32 (N,):  y = x * rstd * (w + offset). */
+int32_t tylo_b200_rms_norm_fwd(void* Y, const void* X, const void* W, float* Rstd,
+                               int64_t M, int64_t N, float eps, float offset, int32_t dtype,
+                               tylo_stream_t stream);
+/* ∇rms_norm! → rms_norm_bwd_dx_partial_dw + rms_norm_bwd_dw (rms_norm.jl:162-185, kernels :34-99).
+ * dW_partial is the fp32 (M, n_groups) scratch `W̄_partial`; it need not be zeroed and no lock
+ * array is used (the reference serialises groups on a spin-lock, :68-78).  Overwrites dX, dW. */
+int32_t tylo_b200_rms_norm_bwd(void* dX, void* dW, const void* dY, const void* X, const void* W,
+                               const float* Rstd, float* dW_partial, int32_t n_groups,
+                               int64_t M, int64_t N, float offset, int32_t dtype,
+                               tylo_stream_t stream);
+
+/* ---- LayerNorm ---------------------------------------------------------------------------------
+ * layer_norm! → layer_norm_fwd (src/norm/layer_norm.jl:157-173, kernel :6-46).
+ * Optional Mean, Rstd fp32 (N,). */
+int32_t tylo_b200_layer_norm_fwd(void* Y, const void* X, const void* W, const void* Bias,
+                                 float* Mean, float* Rstd,
+                                 int64_t M, int64_t N, float eps, int32_t dtype,
+                                 tylo_stream_t stream);
+/* ∇layer_norm! → layer_norm_bwd_dx_partial_dwdb + layer_norm_bwd_dwdb
+ * (layer_norm.jl:207-230, kernels :68-141).  dW_partial, dB_partial fp32 (M, n_groups). */
+int32_t tylo_b200_layer_norm_bwd(void* dX, void* dW, void* dB, const void* dY, const void* X,
+                                 const void* W, const float* Mean, const float* Rstd,
+                                 float* dW_partial, float* dB_partial, int32_t n_groups,
+                                 int64_t M, int64_t N, int32_t dtype, tylo_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TYLO_B200_H */

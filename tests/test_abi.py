@@ -1,0 +1,84 @@
+"""CPU: the shared library loads, exports every symbol the header declares, and validates its
+arguments before touching a device (no compute call is made here)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "tylo_b200.h").read_text()
+DECLARED = sorted(set(re.findall(r"\b(tylo_b200_\w+)\s*\(", HEADER)))
+
+
+def test_header_declares_entry_points():
+    assert len(DECLARED) >= 18
+    for must in ("tylo_b200_attention_fwd", "tylo_b200_attention_bwd", "tylo_b200_flex_attention_fwd",
+                 "tylo_b200_flex_attention_bwd", "tylo_b200_decode_attention", "tylo_b200_softmax_fwd",
+                 "tylo_b200_rms_norm_fwd", "tylo_b200_layer_norm_fwd"):
+        assert must in DECLARED
+
+
+@pytest.mark.parametrize("sym", DECLARED)
+def test_symbol_exported(tylo, sym):
+    lib = ctypes.CDLL(tylo.lib_path())
+    assert hasattr(lib, sym), f"{sym} declared in include/tylo_b200.h but not exported"
+
+
+def test_version_and_status_strings(tylo):
+    assert tylo.version() == 100
+    assert tylo._status_string(0) == "ok"
+    assert "unsupported" in tylo._status_string(2)
+
+
+def _fake(n=1):
+    return ctypes.c_void_p(0x1000 * n)  # aligned, never dereferenced: validation fails first
+
+
+def test_argument_validation_without_device(tylo):
+    lib = tylo._lib
+    # null pointer
+    assert lib.tylo_b200_softmax_fwd(None, _fake(), 8, 8, 0, None) == 1
+    # non-positive extent
+    assert lib.tylo_b200_softmax_fwd(_fake(), _fake(2), 0, 8, 0, None) == 1
+    assert b"positive" in lib.tylo_b200_last_error()
+    # misaligned
+    assert lib.tylo_b200_rms_norm_fwd(ctypes.c_void_p(0x1004), _fake(), _fake(2), None, 8, 8, 1e-5, 0.0, 0, None) == 3
+    # heads not a multiple of kv heads (attention.jl:237)
+    f = _fake
+    rc = lib.tylo_b200_attention_fwd(f(1), f(2), f(3), f(4), None, None, None, None, 64, 64, 16, 16, 3, 2, 1, 0, 0, 0, None)
+    assert rc == 1 and b"multiple" in lib.tylo_b200_last_error()
+    # backward without checkpoints (attention.jl:306: `checkpoints` is required)
+    rc = lib.tylo_b200_attention_bwd(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), None, None, None, f(9), None, 0,
+                                     None, None, 64, 64, 16, 16, 2, 2, 1, 0, 0, 0, None)
+    assert rc == 1 and b"checkpoints" in lib.tylo_b200_last_error()
+    # decode: n_splits must be positive
+    rc = lib.tylo_b200_decode_attention(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), 0, 64, 64, 128, 4, 4, 1, 0, None)
+    assert rc == 1
+    # unknown dtype is rejected before any launch
+    assert lib.tylo_b200_softmax_fwd(_fake(), _fake(2), 8, 8, 7, None) == 1
+
+
+def test_flex_descriptor_validation(tylo):
+    lib = tylo._lib
+    f = _fake
+    md = tylo._MaskDesc(); md.flags = tylo.MASK_DOCUMENT       # document mask without id tables
+    sd = tylo._ScoreDesc()
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
+    assert rc == 1 and b"DocumentMask" in lib.tylo_b200_last_error()
+    md = tylo._MaskDesc(); md.flags = 1 << 9
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
+    assert rc == 2
+    md = tylo._MaskDesc(); sd = tylo._ScoreDesc(); sd.flags = tylo.SCORE_SOFTCAP; sd.cap = 0.0
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
+    assert rc == 1
+
+
+def test_decode_suggest_splits(tylo):
+    n = tylo.decode_suggest_splits(1 << 20, 8, 1)
+    assert n >= 64                      # enough CTAs for a 148-SM part with 8 KV heads
+    assert tylo.decode_suggest_splits(512, 8, 64) >= 1
+    assert tylo.decode_suggest_splits(100, 1, 1) == 1

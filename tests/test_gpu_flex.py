@@ -1,0 +1,149 @@
+"""GPU parity: flex_attention! / ∇flex_attention! against the oracle.  Cases follow
+test/flex.jl:130-210,258-272,283-462 of the reference (fixed mod set)."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import back, check, draw
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(rng, dt, B=2, H=2, Hkv=None, Sq=128, Sk=192, D=64):
+    Hkv = H if Hkv is None else Hkv
+    return (draw(rng, (B, H, Sq, D), dt), draw(rng, (B, Hkv, Sk, D), dt), draw(rng, (B, Hkv, Sk, D), dt))
+
+
+def _mask_cases(t, o):
+    return [
+        ("full", t.FullMask(), None),
+        ("causal", t.CausalMask(), o.MaskSpec(causal=True)),
+        ("sliding window", t.SlidingWindowMask(37), o.MaskSpec(window=37)),
+        ("prefix", t.PrefixMask(50), o.MaskSpec(prefix=50)),
+        ("prefix-lm", t.prefix_lm(50), o.MaskSpec(prefix_or_causal=50)),
+        ("causal & prefix", t.CausalMask() & t.PrefixMask(100), o.MaskSpec(causal=True, prefix=100)),
+    ]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("block_sparse", [True, False])
+@pytest.mark.parametrize("idx", range(6))
+def test_masks(tylo, oracle, idx, block_sparse, dt):
+    name, mod, spec = _mask_cases(tylo, oracle)[idx]
+    (Q, Q64), (K, K64), (V, V64) = _inputs(np.random.default_rng(7), dt)
+    O = tylo.flex_attention(Q, K, V, mask_mod=mod, block_sparse=block_sparse)
+    check(O, oracle.flex_ref(Q64, K64, V64, mask=spec), dt, name)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_input_pos_uneven_gqa_fully_masked(tylo, oracle, dt):
+    rng = np.random.default_rng(17)
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt, Sq=64, Sk=192)
+    O = tylo.flex_attention(Q, K, V, mask_mod=tylo.CausalMask(), input_pos=128)
+    check(O, oracle.flex_ref(Q64, K64, V64, mask=oracle.MaskSpec(causal=True), input_pos=128), dt, "input_pos")
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt, Sq=100, Sk=150)
+    check(tylo.flex_attention(Q, K, V), oracle.flex_ref(Q64, K64, V64), dt, "uneven")
+    check(tylo.flex_attention(Q, K, V, mask_mod=tylo.CausalMask()), oracle.flex_ref(Q64, K64, V64, mask=oracle.MaskSpec(causal=True)), dt, "uneven causal")
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt, H=4, Hkv=2)
+    check(tylo.flex_attention(Q, K, V, mask_mod=tylo.CausalMask()), oracle.flex_ref(Q64, K64, V64, mask=oracle.MaskSpec(causal=True)), dt, "gqa")
+    (Q, _), (K, _), (V, _) = _inputs(rng, dt, Sq=64, Sk=64)
+    cp = tylo.allocate_checkpoints_flex_attention(Q, K, V)
+    for bs in (True, False):
+        O = tylo.flex_attention(Q, K, V, mask_mod=tylo.PrefixMask(0), block_sparse=bs, checkpoints=cp)
+        assert bool((O == 0).all())                               # test/flex.jl:168-173
+        assert bool((cp.L == 0).all()) and bool(torch.isneginf(cp.M).all())   # flex.jl:99-102
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_score_mods(tylo, oracle, dt):
+    rng = np.random.default_rng(27)
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt)
+    H = Q.shape[1]
+    cap = 5.0
+    slopes = torch.tensor([2.0 ** -(i + 1) for i in range(H)], device="cuda")
+    s64 = back(slopes)
+    causal = oracle.MaskSpec(causal=True)
+    O = tylo.flex_attention(Q, K, V, score_mod=tylo.SoftCapScore(cap))
+    check(O, oracle.flex_ref(Q64, K64, V64, score=oracle.ScoreSpec([("softcap", cap)])), dt, "softcap")
+    O = tylo.flex_attention(Q, K, V, score_mod=tylo.AliBiScore(slopes), mask_mod=tylo.CausalMask())
+    check(O, oracle.flex_ref(Q64, K64, V64, score=oracle.ScoreSpec([("alibi", s64)]), mask=causal), dt, "alibi")
+    O = tylo.flex_attention(Q, K, V, score_mod=tylo.SoftCapScore(cap) @ tylo.AliBiScore(slopes), mask_mod=tylo.CausalMask())
+    check(O, oracle.flex_ref(Q64, K64, V64, score=oracle.ScoreSpec([("alibi", s64), ("softcap", cap)]), mask=causal), dt, "softcap∘alibi")
+    O = tylo.flex_attention(Q, K, V, score_mod=tylo.AliBiScore(slopes) @ tylo.SoftCapScore(cap), mask_mod=tylo.CausalMask())
+    check(O, oracle.flex_ref(Q64, K64, V64, score=oracle.ScoreSpec([("softcap", cap), ("alibi", s64)]), mask=causal), dt, "alibi∘softcap")
+    O = tylo.flex_attention(Q, K, V, qk_scale=0.05)
+    check(O, oracle.flex_ref(Q64, K64, V64, qk_scale=0.05), dt, "qk_scale")
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_document_mask(tylo, oracle, dt):
+    rng = np.random.default_rng(37)
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt, Sq=192, Sk=192)
+    docs = np.array([1] * 70 + [2] * 80 + [3] * 42, dtype=np.int32)          # test/flex.jl:258-266
+    dm = tylo.DocumentMask(torch.from_numpy(docs).cuda())
+    check(tylo.flex_attention(Q, K, V, mask_mod=dm), oracle.flex_ref(Q64, K64, V64, mask=oracle.MaskSpec(doc_q=docs)), dt, "document")
+    # per-batch tables (extension) with causal and window
+    tab = np.stack([docs, np.array([5] * 100 + [6] * 92, dtype=np.int32)])
+    dm2 = tylo.CausalMask() & tylo.SlidingWindowMask(64) & tylo.DocumentMask(torch.from_numpy(tab).cuda())
+    O = tylo.flex_attention(Q, K, V, mask_mod=dm2)
+    check(O, oracle.flex_ref(Q64, K64, V64, mask=oracle.MaskSpec(causal=True, window=64), doc_per_batch=tab), dt, "doc per batch")
+
+
+BWD_CASES = ["causal", "causal dense", "gqa window", "uneven", "softcap", "alibi", "compose", "config4-like"]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("case", BWD_CASES)
+def test_backward(tylo, oracle, case, dt):
+    t, o = tylo, oracle
+    rng = np.random.default_rng(11 + len(case))
+    kw = dict(); shape = dict(); okw = dict()
+    slopes = None
+    if case == "causal":
+        kw = dict(mask_mod=t.CausalMask()); okw = dict(mask=o.MaskSpec(causal=True))
+    elif case == "causal dense":
+        kw = dict(mask_mod=t.CausalMask(), block_sparse=False); okw = dict(mask=o.MaskSpec(causal=True))
+    elif case == "gqa window":
+        shape = dict(H=4, Hkv=2); kw = dict(mask_mod=t.SlidingWindowMask(37)); okw = dict(mask=o.MaskSpec(window=37))
+    elif case == "uneven":
+        shape = dict(Sq=100, Sk=150); kw = dict(mask_mod=t.CausalMask()); okw = dict(mask=o.MaskSpec(causal=True))
+    elif case == "softcap":
+        kw = dict(score_mod=t.SoftCapScore(5.0)); okw = dict(score=o.ScoreSpec([("softcap", 5.0)]))
+    elif case in ("alibi", "compose"):
+        slopes = torch.tensor([0.5, 0.25], device="cuda")
+        if case == "alibi":
+            kw = dict(score_mod=t.AliBiScore(slopes), mask_mod=t.CausalMask())
+            okw = dict(score=o.ScoreSpec([("alibi", back(slopes))]), mask=o.MaskSpec(causal=True))
+        else:
+            kw = dict(score_mod=t.SoftCapScore(5.0) @ t.AliBiScore(slopes), mask_mod=t.CausalMask())
+            okw = dict(score=o.ScoreSpec([("alibi", back(slopes)), ("softcap", 5.0)]), mask=o.MaskSpec(causal=True))
+    elif case == "config4-like":
+        shape = dict(B=2, H=2, Sq=256, Sk=256, D=128)
+        tab = np.stack([np.sort(rng.integers(0, 8, 256)).astype(np.int32) for _ in range(2)])
+        kw = dict(mask_mod=t.CausalMask() & t.SlidingWindowMask(64) & t.DocumentMask(torch.from_numpy(tab).cuda()),
+                  score_mod=t.SoftCapScore(50.0))
+        okw = dict(mask=o.MaskSpec(causal=True, window=64), doc_per_batch=tab, score=o.ScoreSpec([("softcap", 50.0)]))
+    (Q, Q64), (K, K64), (V, V64) = _inputs(rng, dt, **shape)
+    cp = t.allocate_checkpoints_flex_attention(Q, K, V)
+    O = t.flex_attention(Q, K, V, checkpoints=cp, **kw)
+    check(O, o.flex_ref(Q64, K64, V64, **okw), dt, f"{case} fwd")
+    dO, dO64 = draw(rng, tuple(O.shape), dt)
+    d_mod = t.grad_shadow(kw["score_mod"]) if slopes is not None else None
+    dQ, dK, dV = t.grad_flex_attention(dO, Q, K, V, O, checkpoints=cp, d_score_mod=d_mod, **kw)
+    rQ, rK, rV, sg = o.flex_bwd_ref(dO64, Q64, K64, V64, **okw)
+    for got, ref, name in ((dQ, rQ, "dQ"), (dK, rK, "dK"), (dV, rV, "dV")):
+        check(got, ref, dt, f"{case} {name}", scale_hint=float(np.abs(ref).max()) / 4)
+    if slopes is not None:
+        got = back(d_mod.slopes if case == "alibi" else d_mod.a.slopes)
+        ref = list(sg.values())[0]
+        np.testing.assert_allclose(got, ref, rtol=2e-2 if dt != "f32" else 1e-4, atol=1e-2 if dt != "f32" else 1e-4)
+
+
+def test_fully_masked_backward_is_exactly_zero(tylo):
+    """test/flex.jl:455-461."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    Q = torch.randn(2, 2, 64, 64, device="cuda", generator=g); K = torch.randn_like(Q); V = torch.randn_like(Q)
+    cp = tylo.allocate_checkpoints_flex_attention(Q, K, V)
+    O = tylo.flex_attention(Q, K, V, mask_mod=tylo.PrefixMask(0), checkpoints=cp)
+    dQ, dK, dV = tylo.grad_flex_attention(torch.randn_like(O), Q, K, V, O, checkpoints=cp, mask_mod=tylo.PrefixMask(0))
+    assert bool((dQ == 0).all()) and bool((dK == 0).all()) and bool((dV == 0).all())

@@ -1,0 +1,752 @@
+"""Python host binding of libtylo_b200 — a mirror of Tylo.jl's exported API.
+
+The production host layer is the Julia package under ``julia/Tylo`` (same directory), whose
+wrappers ``ccall`` the C ABI declared in ``include/tylo_b200.h``.  Julia is not available where
+this library is tested, so this module binds the *same* C ABI through ctypes and mirrors the
+Julia API one to one; the tests and the benchmark drive the kernels through it.
+
+Naming: Julia's ``f!`` is ``f_`` here, ``∇f`` is ``grad_f`` and ``∇f!`` is ``grad_f_``.
+
+Layout: a Julia array of size (D, S, H, B) is column-major; the same bytes are a contiguous
+torch tensor of shape (B, H, S, D).  Every tensor below is given in that reversed-axes form:
+
+    Q (B, H, Sq, Dk)   K (B, Hkv, Sk, Dk)   V (B, Hkv, Sk, Dv)   O (B, H, Sq, Dv)
+    decode: Q (B, H, Dk), O (B, H, Dv), lengths (B,) int32
+    softmax / norms: X (N, M), reduction over the last axis; W, B (M,)
+
+torch is used only for device memory and streams.  There is no CPU implementation and no
+fallback: if the shared library is missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_uint32, c_void_p
+from pathlib import Path
+from typing import NamedTuple, Optional
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_LIB_PATH = Path(os.environ.get("TYLO_B200_LIB", _HERE / "libtylo_b200.so"))
+if not _LIB_PATH.exists():
+    raise ImportError(
+        f"{_LIB_PATH} not found: build it with `python {_HERE / 'build.py'}` "
+        "(libtylo_b200 has no CPU or pure-PyTorch fallback)")
+_lib = ctypes.CDLL(str(_LIB_PATH))
+
+F32, BF16, F16 = 0, 1, 2
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+MASK_CAUSAL, MASK_SLIDING, MASK_DOCUMENT, MASK_PREFIX, MASK_PREFIX_LM = 1, 2, 4, 8, 16
+SCORE_ALIBI, SCORE_SOFTCAP, SCORE_SOFTCAP_FIRST = 1, 2, 4
+
+
+class _MaskDesc(Structure):
+    _fields_ = [("flags", c_uint32), ("window", c_int32), ("prefix_len", c_int32), ("reserved", c_int32),
+                ("doc_q", c_void_p), ("doc_kv", c_void_p), ("doc_batch_stride", c_int64),
+                ("doc_q_len", c_int64), ("doc_kv_len", c_int64)]
+
+
+class _ScoreDesc(Structure):
+    _fields_ = [("flags", c_uint32), ("cap", c_float), ("slopes", c_void_p), ("d_slopes", c_void_p)]
+
+
+class TyloError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libtylo_b200 status {status} ({_status_string(status)}): {message}")
+        self.status = status
+
+
+_lib.tylo_b200_version.restype = c_int32
+_lib.tylo_b200_status_string.restype = c_char_p
+_lib.tylo_b200_status_string.argtypes = [c_int32]
+_lib.tylo_b200_last_error.restype = c_char_p
+_lib.tylo_b200_attention_bwd_workspace_bytes.restype = c_int64
+_lib.tylo_b200_attention_bwd_workspace_bytes.argtypes = [c_int32] * 8
+_lib.tylo_b200_decode_suggest_splits.restype = c_int32
+_lib.tylo_b200_decode_suggest_splits.argtypes = [c_int32] * 3
+
+_i32, _i64, _f32, _ptr = c_int32, c_int64, c_float, c_void_p
+_SIGS = {
+    "tylo_b200_attention_fwd": [_ptr] * 8 + [_i32] * 10 + [_ptr],
+    "tylo_b200_attention_bwd": [_ptr] * 13 + [_i64] + [_ptr] * 2 + [_i32] * 10 + [_ptr],
+    "tylo_b200_flex_attention_fwd": [_ptr] * 6 + [POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
+    "tylo_b200_flex_attention_bwd": [_ptr] * 13 + [_i64, POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
+    "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
+    "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
+    "tylo_b200_decode_combine": [_ptr] * 7 + [_i32, _i64, _i64] + [_i32] * 4 + [_ptr],
+    "tylo_b200_softmax_fwd": [_ptr, _ptr, _i64, _i64, _i32, _ptr],
+    "tylo_b200_softmax_bwd": [_ptr, _ptr, _ptr, _i64, _i64, _i32, _ptr],
+    "tylo_b200_rms_norm_fwd": [_ptr] * 4 + [_i64, _i64, _f32, _f32, _i32, _ptr],
+    "tylo_b200_rms_norm_bwd": [_ptr] * 7 + [_i32, _i64, _i64, _f32, _i32, _ptr],
+    "tylo_b200_layer_norm_fwd": [_ptr] * 6 + [_i64, _i64, _f32, _i32, _ptr],
+    "tylo_b200_layer_norm_bwd": [_ptr] * 10 + [_i32, _i64, _i64, _i32, _ptr],
+}
+for _name, _sig in _SIGS.items():
+    _fn = getattr(_lib, _name)
+    _fn.restype = c_int32
+    _fn.argtypes = _sig
+
+
+def _status_string(status: int) -> str:
+    return _lib.tylo_b200_status_string(status).decode()
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise TyloError(status, _lib.tylo_b200_last_error().decode())
+
+
+def version() -> int:
+    return int(_lib.tylo_b200_version())
+
+
+def lib_path() -> str:
+    return str(_LIB_PATH)
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported element type {t.dtype}") from None
+
+
+def _dense(*ts):
+    for t in ts:
+        if t is not None:
+            if not t.is_cuda:
+                raise ValueError("libtylo_b200 takes device arrays (there is no CPU path)")
+            if not t.is_contiguous():
+                raise ValueError("arrays must be dense")
+
+
+# ---------------------------------------------------------------------------------------------
+# buffer vocabulary (src/buffers.jl)
+# ---------------------------------------------------------------------------------------------
+class Duplicated:
+    """A primal array paired with its gradient buffer (buffers.jl:26-31).  ``Duplicated(x)``
+    allocates an uninitialised shadow (the backward entry points overwrite it)."""
+
+    __slots__ = ("primal", "shadow")
+
+    def __init__(self, primal_, shadow_=None):
+        self.primal = primal_
+        self.shadow = torch.empty_like(primal_) if shadow_ is None else shadow_
+
+
+def primal(x):
+    return x.primal if isinstance(x, Duplicated) else x
+
+
+def shadow(x):
+    return x.shadow
+
+
+# ---------------------------------------------------------------------------------------------
+# mods (src/attention/mods.jl)
+# ---------------------------------------------------------------------------------------------
+class MaskMod:
+    def __and__(self, other):
+        return AndMask(self, other)
+
+    def __or__(self, other):
+        return OrMask(self, other)
+
+
+class FullMask(MaskMod):
+    def __call__(self, b, h, q, kv):
+        return True
+
+
+class CausalMask(MaskMod):
+    def __call__(self, b, h, q, kv):
+        return q >= kv
+
+
+class SlidingWindowMask(MaskMod):
+    def __init__(self, w: int):
+        self.w = int(w)
+
+    def __call__(self, b, h, q, kv):
+        return q >= kv and q <= kv + self.w
+
+
+class PrefixMask(MaskMod):
+    def __init__(self, length: int):
+        self.len = int(length)
+
+    def __call__(self, b, h, q, kv):
+        return kv < self.len
+
+
+class DocumentMask(MaskMod):
+    """Same-document attention.  ``doc`` is an int32 vector indexed by absolute position
+    (mods.jl:141-147).  Extension: a 2-D ``(B, S)`` table gives every batch entry its own ids."""
+
+    def __init__(self, doc_q, doc_kv=None):
+        self.doc_q = doc_q
+        self.doc_kv = doc_q if doc_kv is None else doc_kv
+
+    def __call__(self, b, h, q, kv):
+        dq, dk = self.doc_q, self.doc_kv
+        if dq.dim() == 2:
+            return bool(dq[b - 1, q] == dk[b - 1, kv])
+        return bool(dq[q] == dk[kv])
+
+
+class AndMask(MaskMod):
+    def __init__(self, a, b):
+        self.a, self.b = a, b
+
+    def __call__(self, b, h, q, kv):
+        return self.a(b, h, q, kv) and self.b(b, h, q, kv)
+
+
+class OrMask(MaskMod):
+    def __init__(self, a, b):
+        self.a, self.b = a, b
+
+    def __call__(self, b, h, q, kv):
+        return self.a(b, h, q, kv) or self.b(b, h, q, kv)
+
+
+def prefix_lm(length: int) -> MaskMod:
+    return CausalMask() | PrefixMask(length)
+
+
+class ScoreMod:
+    def __matmul__(self, inner):  # Julia's `outer ∘ inner`
+        return ComposeScore(inner, self)
+
+
+class NoOpScore(ScoreMod):
+    def __call__(self, s, b, h, q, kv):
+        return s
+
+
+class SoftCapScore(ScoreMod):
+    def __init__(self, cap: float):
+        self.cap = float(cap)
+
+    def __call__(self, s, b, h, q, kv):
+        return self.cap * math.tanh(s / self.cap)
+
+
+class AliBiScore(ScoreMod):
+    def __init__(self, slopes: torch.Tensor):
+        self.slopes = slopes
+
+    def __call__(self, s, b, h, q, kv):
+        return s + float(self.slopes[h - 1]) * (q - kv)
+
+
+class ComposeScore(ScoreMod):
+    """Apply ``a`` then ``b`` (mods.jl:244-249)."""
+
+    def __init__(self, a, b):
+        self.a, self.b = a, b
+
+    def __call__(self, s, b, h, q, kv):
+        return self.b(self.a(s, b, h, q, kv), b, h, q, kv)
+
+
+def hmask(m: MaskMod, q: int, kv: int, *, b: int = 1, h: int = 1) -> bool:
+    """Evaluate a mask mod on the host at 0-based positions (mods.jl:53); b, h are 1-based."""
+    return bool(m(b, h, q, kv))
+
+
+def hscore(m: ScoreMod, s: float, q: int, kv: int, *, b: int = 1, h: int = 1) -> float:
+    """Evaluate a score mod on the host (mods.jl:62)."""
+    return float(m(s, b, h, q, kv))
+
+
+def grad_shadow(x):
+    """Zeroed gradient accumulator for an array or a score mod (mods.jl:281-286)."""
+    if isinstance(x, torch.Tensor):
+        return torch.zeros_like(x)
+    if isinstance(x, AliBiScore):
+        return AliBiScore(torch.zeros_like(x.slopes))
+    if isinstance(x, ComposeScore):
+        return ComposeScore(grad_shadow(x.a), grad_shadow(x.b))
+    return x
+
+
+def _unsupported(what):
+    raise TyloError(2, f"{what} is not supported by libtylo_b200 (there is no fallback)")
+
+
+def _mask_desc(m: Optional[MaskMod], keep: list) -> Optional[_MaskDesc]:
+    d = _MaskDesc()
+
+    def walk(x):
+        if x is None or isinstance(x, FullMask):
+            return
+        if isinstance(x, AndMask):
+            walk(x.a); walk(x.b); return
+        if isinstance(x, CausalMask):
+            d.flags |= MASK_CAUSAL; return
+        if isinstance(x, SlidingWindowMask):
+            if d.flags & MASK_SLIDING:
+                d.window = min(d.window, x.w)
+            else:
+                d.flags |= MASK_SLIDING; d.window = x.w
+            return
+        if isinstance(x, PrefixMask):
+            if d.flags & MASK_PREFIX:
+                d.prefix_len = min(d.prefix_len, x.len)
+            elif d.flags & MASK_PREFIX_LM:
+                _unsupported("PrefixMask combined with prefix_lm")
+            else:
+                d.flags |= MASK_PREFIX; d.prefix_len = x.len
+            return
+        if isinstance(x, OrMask):
+            pair = {type(x.a), type(x.b)}
+            if pair == {CausalMask, PrefixMask} and not d.flags & (MASK_PREFIX | MASK_PREFIX_LM):
+                d.flags |= MASK_PREFIX_LM
+                d.prefix_len = x.a.len if isinstance(x.a, PrefixMask) else x.b.len
+                return
+            _unsupported("OrMask other than prefix_lm")
+        if isinstance(x, DocumentMask):
+            if d.flags & MASK_DOCUMENT:
+                _unsupported("more than one DocumentMask")
+            dq, dk = x.doc_q, x.doc_kv
+            if dq.dtype != torch.int32 or dk.dtype != torch.int32:
+                raise TypeError("DocumentMask ids must be int32")
+            _dense(dq, dk)
+            if dq.dim() != dk.dim() or dq.dim() not in (1, 2):
+                raise ValueError("DocumentMask ids must both be vectors or both be (B, S) tables")
+            d.flags |= MASK_DOCUMENT
+            d.doc_q, d.doc_kv = dq.data_ptr(), dk.data_ptr()
+            d.doc_q_len, d.doc_kv_len = dq.shape[-1], dk.shape[-1]
+            if dq.dim() == 2:
+                if dq.shape != dk.shape:
+                    raise ValueError("per-batch DocumentMask tables must have one shape")
+                d.doc_batch_stride = dq.shape[-1]
+            keep.extend([dq, dk])
+            return
+        _unsupported(f"mask mod {type(x).__name__}")
+
+    walk(m)
+    return d
+
+
+def _score_desc(m: Optional[ScoreMod], dm, keep: list) -> _ScoreDesc:
+    d = _ScoreDesc()
+    chain = []
+
+    def walk(x, dx):
+        if x is None or isinstance(x, NoOpScore):
+            return
+        if isinstance(x, ComposeScore):
+            walk(x.a, None if dx is None else dx.a); walk(x.b, None if dx is None else dx.b); return
+        chain.append((x, dx))
+
+    walk(m, dm)
+    for i, (x, dx) in enumerate(chain):
+        if isinstance(x, SoftCapScore):
+            if d.flags & SCORE_SOFTCAP:
+                _unsupported("more than one SoftCapScore")
+            d.flags |= SCORE_SOFTCAP; d.cap = x.cap
+            if not d.flags & SCORE_ALIBI and any(isinstance(y, AliBiScore) for y, _ in chain[i + 1:]):
+                d.flags |= SCORE_SOFTCAP_FIRST
+        elif isinstance(x, AliBiScore):
+            if d.flags & SCORE_ALIBI:
+                _unsupported("more than one AliBiScore")
+            if x.slopes.dtype != torch.float32:
+                raise TypeError("AliBiScore slopes must be float32")
+            _dense(x.slopes)
+            d.flags |= SCORE_ALIBI; d.slopes = x.slopes.data_ptr(); keep.append(x.slopes)
+            if dx is not None:
+                d.d_slopes = dx.slopes.data_ptr(); keep.append(dx.slopes)
+        else:
+            _unsupported(f"score mod {type(x).__name__}")
+    return d
+
+
+# ---------------------------------------------------------------------------------------------
+# attention (src/attention/attention.jl)
+# ---------------------------------------------------------------------------------------------
+class AttnCheckpoints(NamedTuple):
+    M: torch.Tensor
+    L: torch.Tensor
+
+
+class AttnScratch(NamedTuple):
+    dO_scaled: Optional[torch.Tensor]   # the reference's Ō′ (kept for API shape; unused)
+    Delta: torch.Tensor
+    workspace: Optional[torch.Tensor]
+
+
+def _attn_dims(Q, K, V, O=None):
+    if Q.dim() != 4 or K.dim() != 4 or V.dim() != 4:
+        raise ValueError("Q, K, V must be 4-D: (B, H, S, D)")
+    B, H, Sq, Dq = Q.shape
+    Bk, Hkv, Sk, Dk = K.shape
+    Bv, Hv, Sv, Dv = V.shape
+    assert Dq == Dk, "Q and K head dims differ"
+    assert Sk == Sv, "K and V lengths differ"
+    assert Hkv == Hv, "K and V head counts differ"
+    assert B == Bk == Bv, "batch sizes differ"
+    assert H % Hkv == 0, "Heads must be a multiple of Heads_KV"
+    if O is not None:
+        assert tuple(O.shape) == (B, H, Sq, Dv), "O has the wrong shape"
+    if not (Q.dtype == K.dtype == V.dtype):
+        raise TypeError("Q, K, V must share one element type")
+    return B, H, Hkv, Sq, Sk, Dk, Dv
+
+
+def allocate_checkpoints_attention(Q, K, V) -> AttnCheckpoints:
+    """allocate_checkpoints(attention!, Q, K, V) (attention.jl:271-273): fp32 (B, H, Sq)."""
+    B, H, Sq, _ = Q.shape
+    return AttnCheckpoints(torch.empty(B, H, Sq, dtype=torch.float32, device=Q.device),
+                           torch.empty(B, H, Sq, dtype=torch.float32, device=Q.device))
+
+
+def allocate_scratchspace_grad_attention(Q, K, V, O) -> AttnScratch:
+    """allocate_scratchspace(∇attention!, Q, K, V, O) (attention.jl:367-370) plus the
+    library's own workspace."""
+    B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(Q, K, V, O)
+    nbytes = int(_lib.tylo_b200_attention_bwd_workspace_bytes(Dk, Dv, Sq, Sk, H, Hkv, B, _dtype(Q)))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if nbytes > 0 else None
+    return AttnScratch(None, torch.empty(B, H, Sq, dtype=torch.float32, device=Q.device), ws)
+
+
+def attention_(O, Q, K, V, *, causal=False, input_pos=0, k_lengths=None, q_lengths=None, checkpoints=None):
+    """attention!(O, Q, K, V; ...) (attention.jl:219-262).  Returns None."""
+    pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
+    B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
+    _dense(pO, pQ, pK, pV, k_lengths, q_lengths)
+    M = None if checkpoints is None else checkpoints.M
+    L = None if checkpoints is None else checkpoints.L
+    _check(_lib.tylo_b200_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), _p(k_lengths), _p(q_lengths),
+                                        Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos), int(bool(causal)), _dtype(pQ),
+                                        _stream()))
+
+
+def attention(Q, K, V, **kw):
+    """attention(Q, K, V; ...) -> O (attention.jl:281-285)."""
+    O = torch.empty(Q.shape[0], Q.shape[1], Q.shape[2], V.shape[3], dtype=Q.dtype, device=Q.device)
+    attention_(O, Q, K, V, **kw)
+    return O
+
+
+def grad_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplicated, *, causal, checkpoints,
+                    input_pos=0, k_lengths=None, q_lengths=None, scratch=None):
+    """∇attention!(O, Q, K, V; causal, checkpoints, scratch) (attention.jl:297-357)."""
+    pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
+    B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
+    if scratch is None:
+        scratch = allocate_scratchspace_grad_attention(pQ, pK, pV, pO)
+    dO = shadow(O)
+    _dense(pO, pQ, pK, pV, dO, Q.shadow, K.shadow, V.shadow)
+    ws = scratch.workspace
+    _check(_lib.tylo_b200_attention_bwd(_p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV), _p(pO),
+                                        _p(dO), _p(checkpoints.M), _p(checkpoints.L), _p(scratch.dO_scaled),
+                                        _p(scratch.Delta), _p(ws), 0 if ws is None else ws.numel(),
+                                        _p(k_lengths), _p(q_lengths), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
+                                        int(bool(causal)), _dtype(pQ), _stream()))
+
+
+def grad_attention(dO, Q, K, V, O, *, checkpoints, causal, **kw):
+    """∇attention(Ō, Q, K, V, O; checkpoints, causal) -> (Q̄, K̄, V̄) (attention.jl:379-388)."""
+    Qd, Kd, Vd = Duplicated(Q), Duplicated(K), Duplicated(V)
+    grad_attention_(Duplicated(O, dO), Qd, Kd, Vd, checkpoints=checkpoints, causal=causal, **kw)
+    return Qd.shadow, Kd.shadow, Vd.shadow
+
+
+# ---------------------------------------------------------------------------------------------
+# flex attention (src/attention/flex.jl)
+# ---------------------------------------------------------------------------------------------
+allocate_checkpoints_flex_attention = allocate_checkpoints_attention       # flex.jl:391-393
+allocate_scratchspace_grad_flex_attention = allocate_scratchspace_grad_attention  # flex.jl:519-522
+
+
+def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=None, block_sparse=True,
+                    input_pos=0, qk_scale=None, checkpoints=None):
+    """flex_attention!(O, Q, K, V; score_mod, mask_mod, ...) (flex.jl:312-383)."""
+    if block_mask is not None:
+        _unsupported("a host-built BlockMask")
+    pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
+    B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
+    _dense(pO, pQ, pK, pV)
+    keep: list = []
+    md = _mask_desc(mask_mod, keep)
+    sd = _score_desc(score_mod, None, keep)
+    M = None if checkpoints is None else checkpoints.M
+    L = None if checkpoints is None else checkpoints.L
+    _check(_lib.tylo_b200_flex_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md),
+                                             ctypes.byref(sd), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
+                                             0.0 if qk_scale is None else float(qk_scale), int(bool(block_sparse)),
+                                             _dtype(pQ), _stream()))
+
+
+def flex_attention(Q, K, V, **kw):
+    """flex_attention(Q, K, V; score_mod, mask_mod, ...) -> O (flex.jl:430-431)."""
+    O = torch.empty(Q.shape[0], Q.shape[1], Q.shape[2], V.shape[3], dtype=Q.dtype, device=Q.device)
+    flex_attention_(O, Q, K, V, **kw)
+    return O
+
+
+def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplicated, *, checkpoints,
+                         score_mod=None, mask_mod=None, d_score_mod=None, block_sparse=True, input_pos=0,
+                         qk_scale=None, scratch=None):
+    """∇flex_attention!(...; score_mod, mask_mod, ∂score_mod, checkpoints, scratch) (flex.jl:445-511)."""
+    pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
+    B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
+    if scratch is None:
+        scratch = allocate_scratchspace_grad_attention(pQ, pK, pV, pO)
+    dO = shadow(O)
+    _dense(pO, pQ, pK, pV, dO, Q.shadow, K.shadow, V.shadow)
+    keep: list = []
+    md = _mask_desc(mask_mod, keep)
+    sd = _score_desc(score_mod, d_score_mod, keep)
+    ws = scratch.workspace
+    _check(_lib.tylo_b200_flex_attention_bwd(_p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV),
+                                             _p(pO), _p(dO), _p(checkpoints.M), _p(checkpoints.L),
+                                             _p(scratch.dO_scaled), _p(scratch.Delta), _p(ws),
+                                             0 if ws is None else ws.numel(), ctypes.byref(md), ctypes.byref(sd),
+                                             Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
+                                             0.0 if qk_scale is None else float(qk_scale), int(bool(block_sparse)),
+                                             _dtype(pQ), _stream()))
+
+
+def grad_flex_attention(dO, Q, K, V, O, *, checkpoints, **kw):
+    """∇flex_attention(Ō, Q, K, V, O; checkpoints, ...) -> (Q̄, K̄, V̄) (flex.jl:530-539)."""
+    Qd, Kd, Vd = Duplicated(Q), Duplicated(K), Duplicated(V)
+    grad_flex_attention_(Duplicated(O, dO), Qd, Kd, Vd, checkpoints=checkpoints, **kw)
+    return Qd.shadow, Kd.shadow, Vd.shadow
+
+
+# ---------------------------------------------------------------------------------------------
+# decode (src/attention/decode.jl)
+# ---------------------------------------------------------------------------------------------
+class DecodeScratch(NamedTuple):
+    O_partial: torch.Tensor   # (n_splits, B, H, Dv) fp32
+    M_partial: torch.Tensor   # (n_splits, B, H) fp32
+    L_partial: torch.Tensor
+
+
+def decode_suggest_splits(Sk: int, Hkv: int, B: int) -> int:
+    return int(_lib.tylo_b200_decode_suggest_splits(Sk, Hkv, B))
+
+
+def allocate_scratchspace_decode_attention(O, Q, *, n_splits=8) -> DecodeScratch:
+    """allocate_scratchspace(decode_attention!, O, Q; n_splits) (decode.jl:223-231)."""
+    B, H, Dv = O.shape
+    f = dict(dtype=torch.float32, device=O.device)
+    return DecodeScratch(torch.empty(n_splits, B, H, Dv, **f), torch.empty(n_splits, B, H, **f),
+                         torch.empty(n_splits, B, H, **f))
+
+
+def _decode_dims(O, Q, K, V):
+    B, H, Dq = Q.shape
+    Bk, Hkv, Sk, Dk = K.shape
+    Bv, Hv, Sv, Dv = V.shape
+    assert Dq == Dk and Sk == Sv and Hkv == Hv and B == Bk == Bv and H % Hkv == 0
+    if O is not None:
+        assert tuple(O.shape) == (B, H, Dv)
+    return B, H, Hkv, Sk, Dk, Dv
+
+
+def decode_attention_(O, Q, K, V, *, lengths, n_splits=8, scratch=None):
+    """decode_attention!(O, Q, K, V; lengths, n_splits, scratch) -> O (decode.jl:158-212).
+    ``n_splits=None`` asks the library for a count that fills the GPU."""
+    B, H, Hkv, Sk, Dk, Dv = _decode_dims(O, Q, K, V)
+    if scratch is not None:
+        n_splits = scratch.O_partial.shape[0]
+    elif n_splits is None:
+        n_splits = decode_suggest_splits(Sk, Hkv, B)
+    if scratch is None:
+        scratch = allocate_scratchspace_decode_attention(O, Q, n_splits=n_splits)
+    if lengths.dtype != torch.int32:
+        raise TypeError("lengths must be int32")
+    _dense(O, Q, K, V, lengths, *scratch)
+    _check(_lib.tylo_b200_decode_attention(_p(O), _p(Q), _p(K), _p(V), _p(lengths), _p(scratch.O_partial),
+                                           _p(scratch.M_partial), _p(scratch.L_partial), n_splits, Dk, Dv, Sk, H,
+                                           Hkv, B, _dtype(Q), _stream()))
+    return O
+
+
+def decode_split_(Q, K, V, *, lengths, scratch: DecodeScratch):
+    """First half of decode_attention! (mha_decode_split_fwd, decode.jl:187-199)."""
+    B, H, Hkv, Sk, Dk, Dv = _decode_dims(None, Q, K, V)
+    _dense(Q, K, V, lengths, *scratch)
+    _check(_lib.tylo_b200_decode_split(_p(Q), _p(K), _p(V), _p(lengths), _p(scratch.O_partial),
+                                       _p(scratch.M_partial), _p(scratch.L_partial), scratch.O_partial.shape[0],
+                                       Dk, Dv, Sk, H, Hkv, B, _dtype(Q), _stream()))
+
+
+def decode_combine_(O, O_partial, M_partial, L_partial, *, n_splits, o_stride, ml_stride, Dv, H, B,
+                    merged: Optional[DecodeScratch] = None, dtype=None):
+    """Second half (mha_decode_combine, decode.jl:201-209); also merges per-GPU partials."""
+    dt = _dtype(O) if O is not None else (F32 if dtype is None else dtype)
+    mo = mm = ml = None
+    if merged is not None:
+        mo, mm, ml = merged
+    _check(_lib.tylo_b200_decode_combine(_p(O), _p(mo), _p(mm), _p(ml), _p(O_partial), _p(M_partial), _p(L_partial),
+                                         int(n_splits), int(o_stride), int(ml_stride), Dv, H, B, dt, _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# softmax (src/softmax/softmax.jl)
+# ---------------------------------------------------------------------------------------------
+def _mn(X):
+    if X.dim() != 2:
+        raise ValueError("expected a matrix (N, M)")
+    return X.shape[1], X.shape[0]
+
+
+def softmax_(Y, X):
+    """softmax!(Y, X) (softmax.jl:96-105)."""
+    pY, pX = primal(Y), primal(X)
+    M, N = _mn(pX)
+    assert pY.shape == pX.shape and pY.dtype == pX.dtype
+    _dense(pY, pX)
+    _check(_lib.tylo_b200_softmax_fwd(_p(pY), _p(pX), M, N, _dtype(pX), _stream()))
+
+
+def softmax(X):
+    Y = torch.empty_like(X)
+    softmax_(Y, X)
+    return Y
+
+
+def grad_softmax_(Y: Duplicated, X: Duplicated):
+    """∇softmax!(Y, X) (softmax.jl:127-136): X.shadow = y ∘ (ȳ − Σ y∘ȳ)."""
+    M, N = _mn(Y.primal)
+    _dense(Y.primal, Y.shadow, X.shadow)
+    _check(_lib.tylo_b200_softmax_bwd(_p(X.shadow), _p(Y.shadow), _p(Y.primal), M, N, _dtype(Y.primal), _stream()))
+
+
+def grad_softmax(dY, Y):
+    """∇softmax(Ȳ, Y) -> X̄ (softmax.jl:144-148)."""
+    Xd = Duplicated(Y, torch.empty_like(Y))
+    grad_softmax_(Duplicated(Y, dY), Xd)
+    return Xd.shadow
+
+
+# ---------------------------------------------------------------------------------------------
+# RMSNorm / LayerNorm (src/norm/*.jl)
+# ---------------------------------------------------------------------------------------------
+class RmsCheckpoints(NamedTuple):
+    Rstd: torch.Tensor
+
+
+class LnCheckpoints(NamedTuple):
+    Mean: torch.Tensor
+    Rstd: torch.Tensor
+
+
+class RmsScratch(NamedTuple):
+    dW_partial: torch.Tensor   # (n_groups, M) fp32
+
+
+class LnScratch(NamedTuple):
+    dW_partial: torch.Tensor
+    dB_partial: torch.Tensor
+
+
+DEFAULT_N_GROUPS = 296   # two CTAs per SM; the reference's default of 64 leaves most SMs idle
+
+
+def allocate_checkpoints_rms_norm(X, W) -> RmsCheckpoints:
+    return RmsCheckpoints(torch.empty(X.shape[0], dtype=torch.float32, device=X.device))
+
+
+def allocate_checkpoints_layer_norm(X, W, B) -> LnCheckpoints:
+    f = dict(dtype=torch.float32, device=X.device)
+    return LnCheckpoints(torch.empty(X.shape[0], **f), torch.empty(X.shape[0], **f))
+
+
+def allocate_scratchspace_grad_rms_norm(X, W, *, N_GROUPS=DEFAULT_N_GROUPS) -> RmsScratch:
+    return RmsScratch(torch.empty(N_GROUPS, X.shape[1], dtype=torch.float32, device=X.device))
+
+
+def allocate_scratchspace_grad_layer_norm(X, W, B, *, N_GROUPS=DEFAULT_N_GROUPS) -> LnScratch:
+    f = dict(dtype=torch.float32, device=X.device)
+    return LnScratch(torch.empty(N_GROUPS, X.shape[1], **f), torch.empty(N_GROUPS, X.shape[1], **f))
+
+
+def rms_norm_(Y, X, W, *, eps, offset=0.0, checkpoints=None):
+    """rms_norm!(Y, X, W; eps, offset, checkpoints) (rms_norm.jl:115-128)."""
+    pY, pX, pW = primal(Y), primal(X), primal(W)
+    M, N = _mn(pX)
+    assert pY.shape == pX.shape and pW.shape == (M,)
+    _dense(pY, pX, pW)
+    R = None if checkpoints is None else checkpoints.Rstd
+    _check(_lib.tylo_b200_rms_norm_fwd(_p(pY), _p(pX), _p(pW), _p(R), M, N, float(eps), float(offset), _dtype(pX),
+                                       _stream()))
+
+
+def rms_norm(X, W, *, eps, offset=0.0, **kw):
+    Y = torch.empty_like(X)
+    rms_norm_(Y, X, W, eps=eps, offset=offset, **kw)
+    return Y
+
+
+def grad_rms_norm_(Y: Duplicated, X: Duplicated, W: Duplicated, *, checkpoints, offset=0.0, scratch=None):
+    """∇rms_norm!(Y, X, W; checkpoints, scratch, offset) (rms_norm.jl:162-185)."""
+    pX, pW = primal(X), primal(W)
+    M, N = _mn(pX)
+    if scratch is None:
+        scratch = allocate_scratchspace_grad_rms_norm(pX, pW)
+    _dense(pX, pW, Y.shadow, X.shadow, W.shadow, scratch.dW_partial)
+    _check(_lib.tylo_b200_rms_norm_bwd(_p(X.shadow), _p(W.shadow), _p(Y.shadow), _p(pX), _p(pW),
+                                       _p(checkpoints.Rstd), _p(scratch.dW_partial), scratch.dW_partial.shape[0],
+                                       M, N, float(offset), _dtype(pX), _stream()))
+
+
+def grad_rms_norm(dY, X, W, *, checkpoints, offset=0.0, **kw):
+    """∇rms_norm(Ȳ, X, W; checkpoints, offset) -> (X̄, W̄) (rms_norm.jl:206-220)."""
+    Xd, Wd = Duplicated(X), Duplicated(W)
+    grad_rms_norm_(Duplicated(dY, dY), Xd, Wd, checkpoints=checkpoints, offset=offset, **kw)
+    return Xd.shadow, Wd.shadow
+
+
+def layer_norm_(Y, X, W, B, *, eps, checkpoints=None):
+    """layer_norm!(Y, X, W, B; eps, checkpoints) (layer_norm.jl:157-173)."""
+    pY, pX, pW, pB = primal(Y), primal(X), primal(W), primal(B)
+    M, N = _mn(pX)
+    assert pY.shape == pX.shape and pW.shape == (M,) and pB.shape == (M,)
+    _dense(pY, pX, pW, pB)
+    Mean = None if checkpoints is None else checkpoints.Mean
+    R = None if checkpoints is None else checkpoints.Rstd
+    _check(_lib.tylo_b200_layer_norm_fwd(_p(pY), _p(pX), _p(pW), _p(pB), _p(Mean), _p(R), M, N, float(eps),
+                                         _dtype(pX), _stream()))
+
+
+def layer_norm(X, W, B, *, eps, **kw):
+    Y = torch.empty_like(X)
+    layer_norm_(Y, X, W, B, eps=eps, **kw)
+    return Y
+
+
+def grad_layer_norm_(Y: Duplicated, X: Duplicated, W: Duplicated, B: Duplicated, *, checkpoints, scratch=None):
+    """∇layer_norm!(Y, X, W, B; checkpoints, scratch) (layer_norm.jl:207-230)."""
+    pX, pW = primal(X), primal(W)
+    M, N = _mn(pX)
+    if scratch is None:
+        scratch = allocate_scratchspace_grad_layer_norm(pX, pW, primal(B))
+    _dense(pX, pW, Y.shadow, X.shadow, W.shadow, B.shadow, *scratch)
+    _check(_lib.tylo_b200_layer_norm_bwd(_p(X.shadow), _p(W.shadow), _p(B.shadow), _p(Y.shadow), _p(pX), _p(pW),
+                                         _p(checkpoints.Mean), _p(checkpoints.Rstd), _p(scratch.dW_partial),
+                                         _p(scratch.dB_partial), scratch.dW_partial.shape[0], M, N, _dtype(pX),
+                                         _stream()))
+
+
+def grad_layer_norm(dY, X, W, B, *, checkpoints, **kw):
+    """∇layer_norm(Ȳ, X, W, B; checkpoints) -> (X̄, W̄, B̄) (layer_norm.jl:253-268)."""
+    Xd, Wd, Bd = Duplicated(X), Duplicated(W), Duplicated(B)
+    grad_layer_norm_(Duplicated(dY, dY), Xd, Wd, Bd, checkpoints=checkpoints, **kw)
+    return Xd.shadow, Wd.shadow, Bd.shadow

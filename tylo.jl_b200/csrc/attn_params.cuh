@@ -1,0 +1,97 @@
+// Parameters shared by every attention kernel, and the element-wise score/mask mods
+// (device restatement of the mod bodies in src/attention/mods.jl).
+#pragma once
+#include "common.cuh"
+
+namespace tylo {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+  int Dk, Dv, Sq, Sk, H, Hkv, B, G;
+  int input_pos;
+  float scale;            // qk scale applied to the raw dot product
+  uint32_t mask_flags;    // TYLO_MASK_*
+  int window, prefix_len;
+  const int32_t* doc_q;
+  const int32_t* doc_kv;
+  long long doc_stride;   // per-batch stride of the id tables (0 = shared)
+  uint32_t score_flags;   // TYLO_SCORE_*
+  float cap;
+  const float* slopes;
+  float* d_slopes;
+  const int32_t* k_lengths;
+  const int32_t* q_lengths;
+  int natural_stats;      // 1: M/L in natural units (flex), 0: log2 units (attention!)
+  int block_sparse;
+};
+
+// Mask for one (q, kv) pair of absolute 0-based positions (mods.jl:101-167).
+__device__ __forceinline__ bool mask_keep(const AttnParams& p, int b, int q, int kv) {
+  bool keep = true;
+  if (p.mask_flags & TYLO_MASK_CAUSAL) keep = keep && (q >= kv);
+  if (p.mask_flags & TYLO_MASK_SLIDING) keep = keep && (q >= kv) && (q <= kv + p.window);
+  if (p.mask_flags & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
+  if (p.mask_flags & TYLO_MASK_PREFIX_LM) keep = keep && ((q >= kv) || (kv < p.prefix_len));
+  if (p.mask_flags & TYLO_MASK_DOCUMENT)
+    keep = keep && (p.doc_q[(size_t)b * p.doc_stride + q] == p.doc_kv[(size_t)b * p.doc_stride + kv]);
+  return keep;
+}
+
+// Score mod chain on the scaled score s0 (mods.jl:188-249).  Returns the modded score.
+__device__ __forceinline__ float score_apply(const AttnParams& p, float s0, float slope, int q, int kv) {
+  float s = s0;
+  const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
+  const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
+  if (cap && cap_first) s = p.cap * tanhf(s / p.cap);
+  if (alibi) s += slope * (float)(q - kv);
+  if (cap && !cap_first) s = p.cap * tanhf(s / p.cap);
+  return s;
+}
+
+// VJP of the chain at the pre-mod score (mods.jl:288-319): given ds at the output, returns ds0
+// and the value whose sum times (q - kv) is the ALiBi slope gradient.
+__device__ __forceinline__ float score_vjp(const AttnParams& p, float s0, float slope, int q, int kv, float ds,
+                                           float* ds_at_alibi) {
+  const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
+  const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
+  float g = ds;
+  if (cap && !cap_first) {  // softcap is the outer mod: its input is s0 (+ alibi)
+    const float in = alibi ? s0 + slope * (float)(q - kv) : s0;
+    const float th = tanhf(in / p.cap);
+    g *= (1.f - th * th);
+  }
+  *ds_at_alibi = g;         // additive mod passes the gradient through
+  if (cap && cap_first) {
+    const float th = tanhf(s0 / p.cap);
+    g *= (1.f - th * th);
+  }
+  return g;
+}
+
+// Range of key positions [lo, hi) that can hold an unmasked pair for queries [q_lo, q_hi]
+// (absolute positions): the analytic block lattice of mods.jl:345-413 reduced to the affine masks.
+__device__ __forceinline__ void kv_range(const AttnParams& p, int q_lo, int q_hi, int k_len, int* lo, int* hi) {
+  int l = 0, h = k_len;
+  if (p.block_sparse) {
+    if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) h = min(h, q_hi + 1);
+    if (p.mask_flags & TYLO_MASK_SLIDING) l = max(l, q_lo - p.window);
+    if (p.mask_flags & TYLO_MASK_PREFIX) h = min(h, p.prefix_len);
+  }
+  if (h < l) h = l;
+  *lo = l; *hi = h;
+}
+
+// Query range [lo, hi) (row indices, not positions) that can see keys [kv_lo, kv_hi].
+__device__ __forceinline__ void q_range(const AttnParams& p, int kv_lo, int kv_hi, int q_len, int* lo, int* hi) {
+  int l = 0, h = q_len;
+  if (p.block_sparse) {
+    if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) l = max(l, kv_lo - p.input_pos);
+    if (p.mask_flags & TYLO_MASK_SLIDING) h = min(h, kv_hi + p.window - p.input_pos + 1);
+  }
+  if (h < l) h = l;
+  *lo = l; *hi = h;
+}
+
+}  // namespace tylo
