@@ -50,6 +50,13 @@ int32_t tylo_b200_version(void);
 const char* tylo_b200_status_string(int32_t status);
 const char* tylo_b200_last_error(void);
 
+/* Device-side health word of the tensor-core kernels.  Their internal waits (mbarriers between
+ * the copy, MMA and softmax roles) are bounded; a wait that gives up stores a non-zero code and
+ * the kernel drains instead of hanging.  This call synchronises the device, stores the code
+ * (0 = healthy) in *code, clears it, and returns TYLO_ERR_DEVICE_TIMEOUT if it was non-zero.
+ * No counterpart in the reference (its kernels never wait on one another). */
+int32_t tylo_b200_device_status(int32_t* code);
+
 /* ---- mod descriptors (src/attention/mods.jl) -------------------------------------------------
  * The Julia wrapper maps mod *types* to these plain structs by dispatch.  All enabled mask
  * terms are AND-ed (AndMask, mods.jl:151-157).  Positions are 0-based and absolute: query

@@ -65,6 +65,8 @@ _lib.tylo_b200_status_string.argtypes = [c_int32]
 _lib.tylo_b200_last_error.restype = c_char_p
 _lib.tylo_b200_attention_bwd_workspace_bytes.restype = c_int64
 _lib.tylo_b200_attention_bwd_workspace_bytes.argtypes = [c_int32] * 8
+_lib.tylo_b200_device_status.restype = c_int32
+_lib.tylo_b200_device_status.argtypes = [POINTER(c_int32)]
 _lib.tylo_b200_decode_suggest_splits.restype = c_int32
 _lib.tylo_b200_decode_suggest_splits.argtypes = [c_int32] * 3
 
@@ -105,6 +107,14 @@ def version() -> int:
 
 def lib_path() -> str:
     return str(_LIB_PATH)
+
+
+def device_status() -> int:
+    """Synchronises and returns the device-side health word (0 = healthy); raises TyloError with
+    status 6 if a bounded wait inside a tensor-core kernel gave up."""
+    code = c_int32(0)
+    _check(_lib.tylo_b200_device_status(ctypes.byref(code)))
+    return int(code.value)
 
 
 def _p(t: Optional[torch.Tensor]):

@@ -80,6 +80,16 @@ extern "C" int32_t tylo_b200_version(void) { return TYLO_B200_VERSION; }
 
 extern "C" const char* tylo_b200_last_error(void) { return g_err; }
 
+extern "C" int32_t tylo_b200_device_status(int32_t* code) {
+  TYLO_REQUIRE(code, TYLO_ERR_INVALID_ARGUMENT, "device_status: code must be non-null");
+  TYLO_CUDA_OK(cudaDeviceSynchronize());
+  int v = 0;
+  if (int32_t rc = attn_fwd_sm100_status(&v)) return rc;
+  *code = v;
+  TYLO_REQUIRE(v == 0, TYLO_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (code %d)", v);
+  return TYLO_OK;
+}
+
 extern "C" const char* tylo_b200_status_string(int32_t status) {
   switch (status) {
     case TYLO_OK: return "ok";

@@ -19,6 +19,9 @@ bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype);
 int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                        const AttnParams& p, int32_t dtype, cudaStream_t st);
 
+// Reads and clears the device-side status word of the tcgen05 kernels (0 = no bounded wait gave up).
+int32_t attn_fwd_sm100_status(int* out);
+
 int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                           const AttnParams& p, int32_t dtype, cudaStream_t st);
 int64_t attn_bwd_workspace_bytes(int Dk, int Dv, int Sq, int Sk, int H, int Hkv, int B, int32_t dtype);
