@@ -24,6 +24,75 @@ namespace tylo {
     else { constexpr int THREADS = 1024, ITERS = 4; __VA_ARGS__; }                                                    \
   } while (0)
 
+// Merge of two (count, mean, M2) partial statistics.
+__device__ __forceinline__ void welford_merge(float& n, float& mu, float& m2, float nb, float mub, float m2b) {
+  const float nt = n + nb;
+  if (nt > 0.f) {
+    const float d = mub - mu, f = nb / nt;
+    mu += d * f;
+    m2 += m2b + d * d * n * f;
+  }
+  n = nt;
+}
+// Same for partial statistics of EQUAL counts (every thread holds the same number of elements, the
+// common case): no division, `half_n` = elements per side / 2 ... passed as the per-side count.
+template <int THREADS>
+__device__ __forceinline__ void welford_block_equal(float per_thread, float& mu, float& m2, float* scratch) {
+  float n = per_thread;   // elements per side at this level
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float mub = __shfl_xor_sync(0xffffffffu, mu, o), m2b = __shfl_xor_sync(0xffffffffu, m2, o);
+    const float d = mub - mu;
+    mu = 0.5f * (mu + mub);
+    m2 = m2 + m2b + d * d * (0.5f * n);
+    n *= 2.f;
+  }
+  if constexpr (THREADS > 32) {
+    constexpr int kWarps = THREADS / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { scratch[warp] = mu; scratch[32 + warp] = m2; }
+    __syncthreads();
+    mu = scratch[lane & (kWarps - 1)];
+    m2 = scratch[32 + (lane & (kWarps - 1))];
+#pragma unroll
+    for (int o = 1; o < kWarps; o <<= 1) {
+      const float mub = __shfl_xor_sync(0xffffffffu, mu, o), m2b = __shfl_xor_sync(0xffffffffu, m2, o);
+      const float d = mub - mu;
+      mu = 0.5f * (mu + mub);
+      m2 = m2 + m2b + d * d * (0.5f * n);
+      n *= 2.f;
+    }
+  }
+}
+
+// All threads receive the block-wide (count, mean, M2).  `scratch` holds 96 floats.
+template <int THREADS>
+__device__ __forceinline__ void welford_block(float& n, float& mu, float& m2, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float nb = __shfl_xor_sync(0xffffffffu, n, o), mub = __shfl_xor_sync(0xffffffffu, mu, o),
+                m2b = __shfl_xor_sync(0xffffffffu, m2, o);
+    welford_merge(n, mu, m2, nb, mub, m2b);
+  }
+  if constexpr (THREADS > 32) {
+    constexpr int kWarps = THREADS / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { scratch[warp] = n; scratch[32 + warp] = mu; scratch[64 + warp] = m2; }
+    __syncthreads();
+    n = lane < kWarps ? scratch[lane] : 0.f;
+    mu = lane < kWarps ? scratch[32 + lane] : 0.f;
+    m2 = lane < kWarps ? scratch[64 + lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float nb = __shfl_xor_sync(0xffffffffu, n, o), mub = __shfl_xor_sync(0xffffffffu, mu, o),
+                  m2b = __shfl_xor_sync(0xffffffffu, m2, o);
+      welford_merge(n, mu, m2, nb, mub, m2b);
+    }
+  }
+  // the merge is not bit-commutative: every thread takes lane 0's result
+  n = __shfl_sync(0xffffffffu, n, 0); mu = __shfl_sync(0xffffffffu, mu, 0); m2 = __shfl_sync(0xffffffffu, m2, 0);
+}
+
 // ------------------------------------------------------------------------------------------------
 // forward, row in registers
 // ------------------------------------------------------------------------------------------------
@@ -34,6 +103,7 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
                 int M, float eps, float offset) {
   constexpr int VEC = Elem<T>::kVec;
   __shared__ float red[32];
+  __shared__ float wred[LAYER ? 96 : 1];
   const int nvec = M / VEC;
   const size_t row = blockIdx.x;
   RowRegs<T, THREADS, ITERS> x;
@@ -41,26 +111,41 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
 
   const float inv_m = 1.0f / (float)M;
   float mean = 0.f;
+  float ss = 0.f;
   if constexpr (LAYER) {
-    float s = 0.f;
+    // Per-thread mean and centred second moment from the registers, then ONE reduction round that
+    // merges (count, mean, M2) triples (Chan et al.): centred accuracy without a second barrier.
+    float cnt = 0.f, s = 0.f;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
-      float f[VEC]; x.p[i].unpack(f);
+      if (i * THREADS + (int)threadIdx.x < nvec) {
+        float f[VEC]; x.p[i].unpack(f);
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) s += f[j];
+        for (int j = 0; j < VEC; ++j) s += f[j];
+        cnt += (float)VEC;
+      }
     }
-    mean = block_reduce<THREADS>(s, SumOp(), 0.f, red) * inv_m;
-  }
-  float ss = 0.f;
+    float mu = cnt > 0.f ? s / cnt : 0.f, m2 = 0.f;
 #pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    if (i * THREADS + (int)threadIdx.x < nvec) {
-      float f[VEC]; x.p[i].unpack(f);
+    for (int i = 0; i < ITERS; ++i) {
+      if (i * THREADS + (int)threadIdx.x < nvec) {
+        float f[VEC]; x.p[i].unpack(f);
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) { const float c = f[j] - mean; ss += c * c; }
+        for (int j = 0; j < VEC; ++j) { const float c = f[j] - mu; m2 += c * c; }
+      }
     }
+    if (nvec == THREADS * ITERS) welford_block_equal<THREADS>((float)(ITERS * VEC), mu, m2, wred);
+    else welford_block<THREADS>(cnt, mu, m2, wred);
+    mean = mu; ss = m2;
+  } else {
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      float f[VEC]; x.p[i].unpack(f);     // packets past the end are zero
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ss += f[j] * f[j];
+    }
+    ss = block_reduce<THREADS>(ss, SumOp(), 0.f, red);
   }
-  ss = block_reduce<THREADS>(ss, SumOp(), 0.f, red);
   const float rstd = 1.0f / sqrtf(ss * inv_m + eps);
   if (threadIdx.x == 0) {
     if (Rstd) Rstd[row] = rstd;

@@ -47,12 +47,25 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_flag` (shared memory) is polled so that one role's time-out releases
 // every other role of the CTA.  On time-out writes `code` to *status (global) and the flag.
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// instead of returning at once, which keeps waiting warps out of the issue slots of working ones.
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_hint(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;

@@ -143,6 +143,57 @@ softmax_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, int64_t M, int pa
   r.store(Y + row * M + begin, nvec);
 }
 
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Forward for 16-bit storage.  The row stays in registers in its packed 16-bit form (half the
+// registers of an fp32 copy, so twice the bytes in flight per SM for the same occupancy) and exp is
+// evaluated twice per element (once for the sum, once for the output) on the otherwise idle
+// special-function unit; its approximate form is ample for a 16-bit result.
+template <typename T, int THREADS, int ITERS>
+__global__ void __launch_bounds__(THREADS)
+softmax_fwd_packed_kernel(T* __restrict__ Y, const T* __restrict__ X, int64_t M) {
+  constexpr int VEC = Elem<T>::kVec;
+  __shared__ float smem[32];
+  const int nvec = (int)(M / VEC);
+  const size_t row = blockIdx.x;
+  RowRegs<T, THREADS, ITERS> r;
+  r.load(X + row * M, nvec);
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    if (i * THREADS + (int)threadIdx.x < nvec) {
+      float f[VEC]; r.p[i].unpack(f);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) m = fmaxf(m, f[j]);
+    }
+  }
+  m = block_reduce<THREADS>(m, MaxOp(), -INFINITY, smem);
+  const float mo = (m == -INFINITY) ? 0.f : m * kLog2e;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    if (i * THREADS + (int)threadIdx.x < nvec) {
+      float f[VEC]; r.p[i].unpack(f);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) s += ex2_fast(fmaf(f[j], kLog2e, -mo));
+    }
+  }
+  s = block_reduce<THREADS>(s, SumOp(), 0.f, smem);
+  const float inv = s > 0.f ? 1.f / s : 0.f;
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    float f[VEC]; r.p[i].unpack(f);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f[j] = ex2_fast(fmaf(f[j], kLog2e, -mo)) * inv;
+    r.p[i].pack(f);
+  }
+  r.store(Y + row * M, nvec);
+}
+
 template <typename T, int THREADS, int ITERS, bool CLUSTERED>
 __global__ void __launch_bounds__(THREADS)
 softmax_bwd_kernel(T* __restrict__ dX, const T* __restrict__ dY, const T* __restrict__ Y, int64_t M,
@@ -235,9 +286,26 @@ static int32_t softmax_launch(void* out, const void* a, const void* b, int64_t M
   constexpr int VEC = Elem<T>::kVec;
   constexpr int kPartVec = 256 * 4;  // packets per CTA in the clustered shape
   const char* what = FWD ? "softmax_fwd" : "softmax_bwd";
+  if constexpr (FWD && VEC == 8) {
+    if (M % VEC == 0 && M / VEC <= 512 * 16) {
+      const int64_t nv = M / VEC;
+#define TYLO_SMP(THREADS, ITERS)                                                                             \
+  do {                                                                                                       \
+    softmax_fwd_packed_kernel<T, THREADS, ITERS><<<(unsigned)N, THREADS, 0, st>>>((T*)out, (const T*)a, M);  \
+    return check_launch(what);                                                                               \
+  } while (0)
+      if (nv <= 64) TYLO_SMP(32, 2);
+      if (nv <= 256) TYLO_SMP(128, 2);
+      if (nv <= 1024) TYLO_SMP(256, 4);
+      if (nv <= 2048) TYLO_SMP(256, 8);
+      if (nv <= 4096) TYLO_SMP(256, 16);
+      TYLO_SMP(512, 16);
+#undef TYLO_SMP
+    }
+  }
   if (M % VEC == 0) {
     const int64_t nvec = M / VEC;
-#define TYLO_SM_LAUNCH(THREADS, ITERS)                                                                       \
+#define TYLO_SM_LAUNCH(THREADS, ITERS)                                                                      \
   do {                                                                                                       \
     if constexpr (FWD) softmax_fwd_kernel<T, THREADS, ITERS, false><<<(unsigned)N, THREADS, 0, st>>>(          \
         (T*)out, (const T*)a, M, (int)M);                                                                    \
