@@ -115,6 +115,14 @@ C3 = dict(B=4, S=4096, H=32, Hkv=8, D=128)
 C4 = dict(B=2, S=8192, H=16, D=128, window=1024, ndocs=8, cap=50.0)
 C5A = dict(B=64, H=64, Hkv=8, D=128, Smax=32768, lo=1024)
 C5B = dict(B=1, H=64, Hkv=8, D=128, S=1 << 20)
+ROWS = dict(softmax=(4096, 32768), norm=(16384, 8192))
+
+
+def shrink():
+    """--small: same kernels and tile shapes on a few hundred MB, for profiler captures (a capture
+    replays each launch dozens of times; the full-size workloads would take minutes per kernel)."""
+    C3.update(B=1); C4.update(B=1, H=4); C5A.update(B=8); C5B.update(S=1 << 17)
+    ROWS.update(softmax=(1024, 32768), norm=(4096, 8192))
 
 
 def causal_pairs(S):
@@ -246,12 +254,12 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
 def make_rowwise(t, torch, seed, kind):
     g = torch.Generator(device="cuda").manual_seed(seed)
     if kind == "softmax":
-        N, M = 4096, 32768
+        N, M = ROWS["softmax"]
         X = (2 * torch.randn(N, M, device="cuda", generator=g)).to(torch.bfloat16)
         Y = torch.empty_like(X)
         step = lambda: t.softmax_(Y, X)
     else:
-        N, M = 16384, 8192
+        N, M = ROWS["norm"]
         X = torch.randn(N, M, device="cuda", generator=g).to(torch.bfloat16)
         W = (1 + 0.02 * torch.randn(M, device="cuda", generator=g)).to(torch.bfloat16)
         Bv = (0.02 * torch.randn(M, device="cuda", generator=g)).to(torch.bfloat16)
@@ -345,7 +353,11 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--extras", default="", help="comma-separated subset of extras")
+    ap.add_argument("--small", action="store_true", help="reduced sizes for profiler captures (not a bench result)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.small:
+        shrink()
     if args.impl == "reference":
         return run_reference(args)
 
@@ -435,7 +447,9 @@ def main():
             torch.cuda.empty_cache()
         line["extras"] = extras
 
-    if rank == 0 and world == 1:
+    if args.small:
+        line["config"]["small"] = True
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
     if rank == 0:
         print(json.dumps(line))
