@@ -6,9 +6,13 @@ as the checker (or as the timed CPU baseline), never as the thing shipped.
 
 Every function follows one function of the reference's test suite (file:line given in
 each docstring; paths are relative to the Tylo.jl project root).  The reference is a
-Julia package and Julia cannot be run next to this code, so this is a *port*; its
-pins are the formulas and tolerances of the reference tests plus the closed-form
-known-answer vectors under tests/golden/ (generated by tests/golden/make_golden.py).
+Julia package and Julia cannot be run next to this code, so this is a *port*.
+
+PARITY UNPINNED: the reference holds no golden vectors, known-answer tests or fixtures
+for this path, and its own code cannot be executed here to produce any.  What checks
+this port instead are the known-answer vectors under tests/golden/ (an independent
+scalar-loop restatement of the same formulas, tests/golden/make_golden.py), closed-form
+cases and a torch float64 autograd formulation (tests/test_oracle.py).
 
 Array convention: Julia arrays are column-major.  A Julia array of size (D, S, H, B)
 has the same bytes as a C-contiguous NumPy array of shape (B, H, S, D).  All
