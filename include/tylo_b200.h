@@ -196,6 +196,33 @@ int32_t tylo_b200_decode_combine(void* O, float* O_merged, float* M_merged, floa
  * 8*Hkv*B blocks, decode.jl:163,187). */
 int32_t tylo_b200_decode_suggest_splits(int32_t Sk, int32_t Hkv, int32_t B);
 
+/* decode_attention for callers that cannot supply scratch.  This entry has no counterpart in the
+ * reference (there the scratch is always a caller-owned array, decode.jl:164,223-231).
+ *
+ * Who needs it: host code that may not allocate device memory at the point of the call — a
+ * serving loop whose memory pool is frozen after start-up, a plugin inside a runtime that owns
+ * all device memory, a callback without an allocator — and that has no spare buffer to pass.
+ * Same arguments and result as tylo_b200_decode_attention, minus the three partial buffers: the
+ * split partials are kept in a fixed fp32 array inside the library image
+ * (tylo_b200_decode_static_scratch_floats() elements = 8 MiB, resident on every GPU that loads the
+ * library, from load until the process exits).  The call allocates nothing and frees nothing.
+ *
+ *  - Limit: n_splits * B * H * (Dv + 2) must not exceed that element count; a larger request is
+ *    refused with TYLO_ERR_WORKSPACE and a message (nothing is launched).
+ *  - The first call on each device looks up the array's device address (a host-side symbol
+ *    query, no allocation) with that device current; make that first call outside any stream
+ *    capture.
+ *  - All calls on a device share the one array and it keeps whatever the previous call left.
+ *    The kernels overwrite every slot they later read, so no clearing is needed, but two calls
+ *    whose GPU work overlaps (different streams, no ordering between them) race on it: order
+ *    them on one stream or with events. */
+int32_t tylo_b200_decode_attention_static(void* O, const void* Q, const void* K, const void* V,
+                                          const int32_t* lengths, int32_t n_splits,
+                                          int32_t Dk, int32_t Dv, int32_t Sk,
+                                          int32_t H, int32_t Hkv, int32_t B,
+                                          int32_t dtype, tylo_stream_t stream);
+int64_t tylo_b200_decode_static_scratch_floats(void);
+
 /* ---- softmax -----------------------------------------------------------------------------------
  * softmax! → softmax_fwd / softmax_fwd_single (src/softmax/softmax.jl:96-105, kernels :6-33,:62-72).
  * X, Y (M,N): softmax along dim 1 (the contiguous one), one column per n. */

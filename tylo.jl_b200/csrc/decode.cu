@@ -554,3 +554,62 @@ extern "C" int32_t tylo_b200_decode_attention(void* O, const void* Q, const void
   return tylo_b200_decode_combine(O, nullptr, nullptr, nullptr, O_partial, M_partial, L_partial, n_splits,
                                   (int64_t)H * B * Dv, (int64_t)H * B, Dv, H, B, dtype, stream);
 }
+
+// ---- decode without caller-provided scratch ------------------------------------------------------------
+// Some hosts cannot hand the library a scratch buffer: code running where cudaMalloc is off limits —
+// a serving loop that has frozen its memory pool, a plugin called from a runtime that owns every
+// byte of device memory, a callback with no allocator in reach.  For them the split partials live in
+// a fixed array that is part of the library image on every GPU that loads it.
+//
+// The array's name is only a host-side handle: its device address is looked up once per device with
+// cudaGetSymbolAddress (while that device is current) and that address is what the kernels receive.
+namespace tylo {
+
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;   // 8 MiB of fp32, held from load until exit
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_addr[kMaxDevices] = {};
+
+// First call on a device resolves the address (no allocation); later calls reuse it.
+static int32_t static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  TYLO_CUDA_OK(cudaGetDevice(&dev));
+  TYLO_REQUIRE(dev >= 0 && dev < kMaxDevices, TYLO_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  float* p = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    TYLO_CUDA_OK(cudaGetSymbolAddress(&sym, g_decode_static_scratch));
+    TYLO_REQUIRE(sym != nullptr, TYLO_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    p = static_cast<float*>(sym);
+    __atomic_store_n(&g_static_scratch_addr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return TYLO_OK;
+}
+
+}  // namespace tylo
+
+extern "C" int64_t tylo_b200_decode_static_scratch_floats(void) { return (int64_t)tylo::kStaticScratchFloats; }
+
+extern "C" int32_t tylo_b200_decode_attention_static(void* O, const void* Q, const void* K, const void* V,
+                                                     const int32_t* lengths, int32_t n_splits, int32_t Dk,
+                                                     int32_t Dv, int32_t Sk, int32_t H, int32_t Hkv, int32_t B,
+                                                     int32_t dtype, tylo_stream_t stream) {
+  TYLO_REQUIRE(O, TYLO_ERR_INVALID_ARGUMENT, "decode_attention_static: O must be non-null");
+  if (int32_t rc = check_decode_dims("decode_attention_static", n_splits, Dk, Dv, Sk, H, Hkv, B)) return rc;
+  const int64_t need = (int64_t)n_splits * B * H * ((int64_t)Dv + 2);
+  TYLO_REQUIRE(need <= (int64_t)kStaticScratchFloats, TYLO_ERR_WORKSPACE,
+               "decode_attention_static: n_splits*B*H*(Dv+2) = %lld floats exceeds the built-in scratch of %lld "
+               "floats; lower n_splits or use tylo_b200_decode_attention with your own scratch",
+               (long long)need, (long long)kStaticScratchFloats);
+  float* base = nullptr;
+  if (int32_t rc = static_scratch_for_current_device(&base)) return rc;
+  // every (split, batch, head) slot is overwritten by the split kernel, so nothing has to be cleared
+  const size_t n_o = (size_t)n_splits * B * H * Dv, n_ml = (size_t)n_splits * B * H;
+  float* o_part = base;
+  float* m_part = base + n_o;
+  float* l_part = m_part + n_ml;
+  return tylo_b200_decode_attention(O, Q, K, V, lengths, o_part, m_part, l_part, n_splits, Dk, Dv, Sk, H, Hkv, B,
+                                    dtype, stream);
+}
