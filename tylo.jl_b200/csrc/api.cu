@@ -85,6 +85,11 @@ extern "C" int32_t tylo_b200_device_status(int32_t* code) {
   TYLO_CUDA_OK(cudaDeviceSynchronize());
   int v = 0;
   if (int32_t rc = attn_fwd_sm100_status(&v)) return rc;
+  if (v == 0) {
+    int w = 0;
+    if (int32_t rc = attn_bwd_sm100_status(&w)) return rc;
+    if (w != 0) v = 1000 + w;   // backward kernels report 1000 + their own code
+  }
   *code = v;
   TYLO_REQUIRE(v == 0, TYLO_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (code %d)", v);
   return TYLO_OK;

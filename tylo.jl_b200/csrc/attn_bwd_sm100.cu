@@ -1,0 +1,548 @@
+// Flash-attention backward for sm_100a on tcgen05 / TMEM / TMA, as two launches of one template.
+//
+//   mode DKDV  one CTA owns 128 keys of one KV head and streams the query tiles that can see them
+//              (all G query heads of the group in turn).  Everything is computed TRANSPOSED so that
+//              TMEM lanes are keys:
+//                 T1 = K Q^T  (= S^T)        T2 = V dO^T (= dP^T)        both operands in shared memory
+//                 U1 = P^T,  U2 = dS^T       written back over T1 / T2 as 16-bit
+//                 dV += U1 dO                dK += U2 Q                  A from tensor memory (full rate)
+//              dK and dV stay in TMEM over the whole group: the GQA sum is fp32 and needs no atomics.
+//   mode DQ    one CTA owns 128 queries of one head and streams the key tiles: T1 = Q K^T, T2 = dO V^T,
+//              U2 = dS, dQ += U2 K.
+//
+// Recomputing S and dP in both modes costs 7 tile MMAs per (q,kv) tile pair instead of 5, and in
+// exchange there is no fp32 dQ workspace, no atomic traffic, no zero-fill, and results are
+// bit-repeatable (the reference read-modify-writes dQ in the storage type per tile and uses
+// storage-type atomics for GQA: attention.jl:185-194).
+//
+// Roles per CTA (384 threads): warp 0 = producer (TMA tiles; in DKDV also the per-query statistics
+// of each streamed tile), warp 1 = MMA issuer and TMEM owner, warps 4-7 and 8-11 = two compute
+// warpgroups that split the 128 columns of T1/T2 in halves; thread r of each owns TMEM lane r.
+// P uses the forward's saved statistics through lse2 = log2-domain log-sum-exp, so the element work
+// has no reductions: p = exp2(t - lse2), ds = p (dp - Delta).
+//
+// TMEM columns: [0,128) T1/U1, [128,256) T2/U2, [256,256+D) acc1 (dV), [384,384+D) acc2 (dK or dQ).
+// No multicast, no clusters; every wait is bounded (see sm100_ptx.cuh).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "attn_dispatch.cuh"
+#include "sm100_ptx.cuh"
+
+namespace tylo {
+using namespace sm100;
+
+__device__ int g_attn_bwd_status = 0;
+
+namespace bwd {
+
+constexpr int BT = 128;            // tile edge (queries and keys)
+constexpr int kThreads = 384;
+constexpr int kStages = 2;
+enum Mode { DKDV = 0, DQ = 1 };
+
+template <int D> struct Smem {
+  static constexpr int kTile = BT * D * 2;
+  static constexpr int kX = 0;                               // two stationary tiles
+  static constexpr int kY = 2 * kTile;                       // ring of (Y1, Y2) pairs
+  static constexpr int kStats = kY + kStages * 2 * kTile;    // per stage: lse2[128], delta[128], doc[128]
+  static constexpr int kStatStage = 3 * BT * 4;
+  static constexpr int kBars = kStats + kStages * kStatStage;
+  static constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + kStages, STAT_FULL = Y_EMPTY + kStages,
+                       T_FULL = STAT_FULL + kStages, T_READ = T_FULL + 1, U_FULL = T_READ + 1, DONE = U_FULL + 1,
+                       kNumBars = DONE + 1;
+  static constexpr int kMisc = kBars + 8 * kNumBars;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+template <> struct Fmt<__half> { static constexpr int v = 0; };
+
+template <typename T> __device__ __forceinline__ uint32_t pack16(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <> __device__ __forceinline__ uint32_t pack16<__half>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// tanh(x): odd polynomial on the FMA pipe for small |x|, hardware approximation otherwise
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float x2 = x * x;
+  float t;
+  if (x2 < 0.16f) t = x * fmaf(x2, fmaf(x2, fmaf(x2, -0.05396825f, 0.13333334f), -0.33333334f), 1.f);
+  else asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+__device__ __forceinline__ void tmem_st32x(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// p and the scaled pre-mod score gradient for one element.
+//   s   : raw dot product q.k          dp : dO.v          lse2 / delta : statistics of the query
+// Returns p; ds0 (already multiplied by the qk scale) through the reference.
+template <bool MODDED, bool PARTIAL>
+__device__ __forceinline__ float element(const AttnParams& p, float c, float slope, float inv_cap, float s, float dp,
+                                         float lse2, float delta, int qpos, int kv, bool row_ok, int doc_q, int doc_kv,
+                                         float& ds0) {
+  float pv, f = p.scale;
+  if (MODDED) {
+    float s0 = s * p.scale, sm = s0;
+    const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
+    const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
+    if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
+    if (alibi) sm = fmaf(slope, (float)(qpos - kv), sm);
+    if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
+    pv = ex2(fmaf(sm, kLog2e, -lse2));
+  } else {
+    pv = ex2(fmaf(s, c, -lse2));
+  }
+  if (PARTIAL) {
+    bool keep = row_ok && (kv < p.Sk) && (qpos - p.input_pos < p.Sq);
+    const uint32_t m = p.mask_flags;
+    if (m & TYLO_MASK_CAUSAL) keep = keep && (qpos >= kv);
+    if (m & TYLO_MASK_SLIDING) keep = keep && (qpos >= kv) && (qpos <= kv + p.window);
+    if (m & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
+    if (m & TYLO_MASK_PREFIX_LM) keep = keep && ((qpos >= kv) || (kv < p.prefix_len));
+    if (m & TYLO_MASK_DOCUMENT) keep = keep && (doc_q == doc_kv);
+    if (!keep) pv = 0.f;
+  }
+  ds0 = pv * (dp - delta) * f;
+  return pv;
+}
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ lse2g,
+                      const float* __restrict__ deltag, const AttnParams p) {
+  using SM = Smem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_addr(smem);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMisc + 4);
+  auto bar = [&](int i) { return sbase + SM::kBars + 8 * i; };
+  auto stat = [&](int s, int which) { return reinterpret_cast<float*>(smem + SM::kStats + s * SM::kStatStage + which * BT * 4); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- what this CTA owns and which tiles it streams
+  int b, h0, hk, own0;       // own0: first row (key or query) of the owned tile
+  int it_lo, it_n, n_iter;   // streamed tile range [it_lo, it_lo + it_n) per head; n_iter over the group
+  if (MODE == DKDV) {
+    const int nkt = (p.Sk + BT - 1) / BT;
+    const int kt = blockIdx.x % nkt, hkb = blockIdx.x / nkt;
+    b = hkb / p.Hkv; hk = hkb % p.Hkv; h0 = hk * p.G; own0 = kt * BT;
+    int lo, hi;
+    q_range(p, own0, min(own0 + BT, p.Sk) - 1, p.Sq, &lo, &hi);
+    it_lo = lo / BT; it_n = hi > lo ? (hi - 1) / BT - it_lo + 1 : 0;
+    n_iter = it_n * p.G;
+  } else {
+    const int nqt = (p.Sq + BT - 1) / BT;
+    const int qt = nqt - 1 - (int)(blockIdx.x % nqt), hb = blockIdx.x / nqt;
+    b = hb / p.H; h0 = hb % p.H; hk = h0 / p.G; own0 = qt * BT;
+    int lo, hi;
+    kv_range(p, own0 + p.input_pos, min(own0 + BT, p.Sq) - 1 + p.input_pos, p.Sk, &lo, &hi);
+    it_lo = lo / BT; it_n = hi > lo ? (hi - 1) / BT - it_lo + 1 : 0;
+    n_iter = it_n;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(SM::X_FULL), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(SM::Y_FULL + s), 1); mbar_init(bar(SM::Y_EMPTY + s), 1); mbar_init(bar(SM::STAT_FULL + s), 32);
+    }
+    mbar_init(bar(SM::T_FULL), 1); mbar_init(bar(SM::T_READ), 256); mbar_init(bar(SM::U_FULL), 256);
+    mbar_init(bar(SM::DONE), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0 && n_iter > 0) {
+      // ------------------------------------------------------------------ producer (whole warp)
+      if (lane == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+        mbar_expect_tx(bar(SM::X_FULL), 2 * SM::kTile);
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {
+          if (MODE == DKDV) {
+            tma_load_3d(sbase + SM::kX + cc * (BT * 128), &tmK, bar(SM::X_FULL), cc * 64, own0, b * p.Hkv + hk);
+            tma_load_3d(sbase + SM::kX + SM::kTile + cc * (BT * 128), &tmV, bar(SM::X_FULL), cc * 64, own0, b * p.Hkv + hk);
+          } else {
+            tma_load_3d(sbase + SM::kX + cc * (BT * 128), &tmQ, bar(SM::X_FULL), cc * 64, own0, b * p.H + h0);
+            tma_load_3d(sbase + SM::kX + SM::kTile + cc * (BT * 128), &tmdO, bar(SM::X_FULL), cc * 64, own0, b * p.H + h0);
+          }
+        }
+      }
+      bool ok = true;
+      for (int n = 0; n < n_iter && ok; ++n) {
+        const int s = n % kStages;
+        const int g = (MODE == DKDV) ? n / it_n : 0;
+        const int tile = it_lo + ((MODE == DKDV) ? n % it_n : n);
+        const int row0 = tile * BT;
+        if (n >= kStages)
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::Y_EMPTY + s), ((n / kStages) - 1) & 1, abort_flag, &g_attn_bwd_status, 101));
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(bar(SM::Y_FULL + s), 2 * SM::kTile);
+          const uint32_t y1 = sbase + SM::kY + s * 2 * SM::kTile, y2 = y1 + SM::kTile;
+#pragma unroll
+          for (int cc = 0; cc < D / 64; ++cc) {
+            if (MODE == DKDV) {
+              tma_load_3d(y1 + cc * (BT * 128), &tmQ, bar(SM::Y_FULL + s), cc * 64, row0, b * p.H + h0 + g);
+              tma_load_3d(y2 + cc * (BT * 128), &tmdO, bar(SM::Y_FULL + s), cc * 64, row0, b * p.H + h0 + g);
+            } else {
+              tma_load_3d(y1 + cc * (BT * 128), &tmK, bar(SM::Y_FULL + s), cc * 64, row0, b * p.Hkv + hk);
+              tma_load_3d(y2 + cc * (BT * 128), &tmV, bar(SM::Y_FULL + s), cc * 64, row0, b * p.Hkv + hk);
+            }
+          }
+        }
+        // statistics / document ids of the streamed tile's positions
+        float* slse = stat(s, 0); float* sdel = stat(s, 1); int* sdoc = reinterpret_cast<int*>(stat(s, 2));
+        for (int idx = lane; idx < BT; idx += 32) {
+          const int row = row0 + idx;
+          if (MODE == DKDV) {
+            const bool valid = row < p.Sq;
+            const size_t si = (size_t)(b * p.H + h0 + g) * p.Sq + (valid ? row : 0);
+            slse[idx] = valid ? lse2g[si] : INFINITY;
+            sdel[idx] = valid ? deltag[si] : 0.f;
+            sdoc[idx] = (p.mask_flags & TYLO_MASK_DOCUMENT) ? p.doc_q[(size_t)b * p.doc_stride + min(row, p.Sq - 1) + p.input_pos] : 0;
+          } else {
+            sdoc[idx] = (p.mask_flags & TYLO_MASK_DOCUMENT) ? p.doc_kv[(size_t)b * p.doc_stride + min(row, p.Sk - 1)] : 0;
+          }
+        }
+        mbar_arrive(bar(SM::STAT_FULL + s));
+      }
+    } else if (warp == 1 && lane == 0 && n_iter > 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc_ss = idesc_f16(Fmt<T>::v, 0, 0, BT, BT);
+      constexpr uint32_t idesc_ts = idesc_f16(Fmt<T>::v, 0, 1, BT, D);
+      const uint64_t dk_hi = smem_desc_sw128(0, 16, 1024);            // K-major operand
+      const uint64_t dmn_hi = smem_desc_sw128(0, BT * 128, 1024);     // MN-major operand
+      auto desc_at = [](uint64_t hi, uint32_t saddr) { return hi | (uint64_t)((saddr & 0x3ffff) >> 4); };
+      const uint32_t x1 = sbase + SM::kX, x2 = x1 + SM::kTile;
+      auto issue_t = [&](int n) {
+        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile, y2 = y1 + SM::kTile;
+        const uint64_t a1 = desc_at(dk_hi, x1), a2 = desc_at(dk_hi, x2), b1 = desc_at(dk_hi, y1), b2 = desc_at(dk_hi, y2);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = ((k / 4) * (BT * 128) + (k % 4) * 32) >> 4;
+          mma_ss(tmem, a1 + off, b1 + off, idesc_ss, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = ((k / 4) * (BT * 128) + (k % 4) * 32) >> 4;
+          mma_ss(tmem + 128, a2 + off, b2 + off, idesc_ss, k > 0);
+        }
+        tc_commit(bar(SM::T_FULL));
+      };
+      auto issue_acc = [&](int n) {
+        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile, y2 = y1 + SM::kTile;
+        const uint64_t b1 = desc_at(dmn_hi, y1), b2 = desc_at(dmn_hi, y2);
+        if (MODE == DKDV) {
+#pragma unroll
+          for (int k = 0; k < BT / 16; ++k)
+            mma_ts(tmem + 256, tmem + k * 8, b2 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
+        }
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k)
+          mma_ts(tmem + 384, tmem + 128 + k * 8, b1 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
+        tc_commit(bar(SM::Y_EMPTY + (n % kStages)));
+      };
+      bool ok = mbar_wait(bar(SM::X_FULL), 0, abort_flag, &g_attn_bwd_status, 201);
+      ok = ok && mbar_wait(bar(SM::Y_FULL + 0), 0, abort_flag, &g_attn_bwd_status, 202);
+      if (ok) { tc_fence_after(); issue_t(0); }
+      for (int n = 0; n < n_iter && ok; ++n) {
+        ok = mbar_wait(bar(SM::U_FULL), n & 1, abort_flag, &g_attn_bwd_status, 203);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(n);
+        if (n + 1 < n_iter) {
+          ok = mbar_wait(bar(SM::Y_FULL + (n + 1) % kStages), ((n + 1) / kStages) & 1, abort_flag, &g_attn_bwd_status, 204);
+          if (!ok) break;
+          tc_fence_after();
+          issue_t(n + 1);
+        }
+      }
+      tc_commit(bar(SM::DONE));
+      mbar_drain(bar(SM::DONE), 0);
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ------------------------------------------------------------------ compute warpgroups
+    const int wg = (warp - 4) >> 2;                 // column half
+    const int r = (warp & 3) * 32 + lane;           // TMEM lane = row of the owned tile
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int own_row = own0 + r;
+    const bool modded = p.score_flags != 0;
+    const float c = p.scale * kLog2e;
+    const float inv_cap = 1.f / p.cap;
+    const bool has_doc = p.mask_flags & TYLO_MASK_DOCUMENT;
+    // per-thread constants of the owned row
+    float my_lse = INFINITY, my_delta = 0.f, slope = 0.f;
+    int my_doc = 0;
+    if (MODE == DQ) {
+      if (own_row < p.Sq) {
+        const size_t si = (size_t)(b * p.H + h0) * p.Sq + own_row;
+        my_lse = lse2g[si]; my_delta = deltag[si];
+      }
+      if (has_doc) my_doc = p.doc_q[(size_t)b * p.doc_stride + min(own_row, p.Sq - 1) + p.input_pos];
+      if (p.score_flags & TYLO_SCORE_ALIBI) slope = p.slopes[h0];
+    } else if (has_doc) {
+      my_doc = p.doc_kv[(size_t)b * p.doc_stride + min(own_row, p.Sk - 1)];
+    }
+    const bool row_ok = (MODE == DKDV) ? (own_row < p.Sk) : (own_row < p.Sq);
+
+    bool ok = true;
+    for (int n = 0; n < n_iter && ok; ++n) {
+      const int s = n % kStages;
+      const int g = (MODE == DKDV) ? n / it_n : 0;
+      const int tile0 = (it_lo + ((MODE == DKDV) ? n % it_n : n)) * BT;
+      if (MODE == DKDV && (p.score_flags & TYLO_SCORE_ALIBI)) slope = p.slopes[h0 + g];
+      const int qa = (MODE == DKDV) ? tile0 : own0, ka = (MODE == DKDV) ? own0 : tile0;
+      bool partial = (ka + BT > p.Sk) || (qa + BT > p.Sq) || has_doc || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
+      if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) partial = partial || (ka + BT - 1 > qa + p.input_pos);
+      if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
+
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
+      ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld32(tmem + lane_off + 64 * wg, sv[0]); tmem_ld32(tmem + lane_off + 64 * wg + 32, sv[1]);
+      tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(SM::T_READ));
+
+      const float* slse = stat(s, 0); const float* sdel = stat(s, 1); const int* sdoc = reinterpret_cast<const int*>(stat(s, 2));
+      uint32_t up[32], ud[32];
+      auto run = [&](auto modded_c, auto partial_c) {
+        constexpr bool MOD = decltype(modded_c)::value, PART = decltype(partial_c)::value;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+#pragma unroll
+          for (int t = 0; t < 32; t += 2) {
+            float pp[2], dd[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int col = 64 * wg + q * 32 + t + e;
+              const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
+              const int kv = (MODE == DKDV) ? own_row : tile0 + col;
+              const float lse = (MODE == DKDV) ? slse[col] : my_lse;
+              const float del = (MODE == DKDV) ? sdel[col] : my_delta;
+              const int dq = (MODE == DKDV) ? (PART ? sdoc[col] : 0) : my_doc;
+              const int dk = (MODE == DKDV) ? my_doc : (PART ? sdoc[col] : 0);
+              pp[e] = element<MOD, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
+                                         lse, del, qpos, kv, row_ok, dq, dk, dd[e]);
+            }
+            up[q * 16 + t / 2] = pack16<T>(pp[0], pp[1]);
+            ud[q * 16 + t / 2] = pack16<T>(dd[0], dd[1]);
+          }
+        }
+      };
+      if (modded) { if (partial) run(std::true_type{}, std::true_type{}); else run(std::true_type{}, std::false_type{}); }
+      else { if (partial) run(std::false_type{}, std::true_type{}); else run(std::false_type{}, std::false_type{}); }
+
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T_READ), n & 1, abort_flag, &g_attn_bwd_status, 303));
+      if (!ok) break;
+      tc_fence_after();
+      if (MODE == DKDV) tmem_st32x(tmem + lane_off + 32 * wg, up);
+      tmem_st32x(tmem + 128 + lane_off + 32 * wg, ud);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(SM::U_FULL));
+    }
+
+    // ---- epilogue: this warpgroup stores columns [wg*D/2, (wg+1)*D/2) of each accumulator
+    if (n_iter > 0 && ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::DONE), 0, abort_flag, &g_attn_bwd_status, 304));
+      tc_fence_after();
+    }
+    if (ok) {
+      constexpr int HALF = D / 2;
+      const size_t orow = (MODE == DKDV) ? ((size_t)(b * p.Hkv + hk) * p.Sk + (row_ok ? own_row : 0))
+                                         : ((size_t)(b * p.H + h0) * p.Sq + (row_ok ? own_row : 0));
+#pragma unroll
+      for (int a = (MODE == DKDV ? 0 : 1); a < 2; ++a) {
+        T* dst = ((MODE == DKDV) ? (a == 0 ? out1 : out2) : out1) + orow * D + wg * HALF;
+#pragma unroll
+        for (int q = 0; q < HALF / 32; ++q) {
+          uint32_t acc[32];
+          if (n_iter > 0) { tmem_ld32(tmem + 256 + a * 128 + lane_off + wg * HALF + q * 32, acc); tc_wait_ld(); }
+          uint4 o4[4];
+          uint32_t* ow = reinterpret_cast<uint32_t*>(o4);
+#pragma unroll
+          for (int t = 0; t < 16; ++t)
+            ow[t] = (n_iter > 0) ? pack16<T>(__uint_as_float(acc[2 * t]), __uint_as_float(acc[2 * t + 1])) : 0u;
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + q * 32 + v * 8) = o4[v];
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0 && lane == 0 && n_iter > 0) {
+    mbar_drain(bar(SM::X_FULL), 0);
+    for (int s = 0; s < kStages && s < n_iter; ++s) {
+      const int last = ((n_iter - 1 - s) / kStages) * kStages + s;
+      mbar_drain(bar(SM::Y_FULL + s), (last / kStages) & 1);
+    }
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// Delta[row] = sum_d dO*O and lse2[row] = log2-domain log-sum-exp from the forward's (M, L).
+template <typename T>
+__global__ void __launch_bounds__(256)
+bwd_prep_kernel(float* __restrict__ Delta, float* __restrict__ lse2, const T* __restrict__ O,
+                const T* __restrict__ dO, const float* __restrict__ M, const float* __restrict__ L,
+                long long rows, int Dv, int natural_stats) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int d = lane * 8; d < Dv; d += 256) {
+    Pack<T> a, b2;
+    a.raw = *reinterpret_cast<const uint4*>(O + (size_t)row * Dv + d);
+    b2.raw = *reinterpret_cast<const uint4*>(dO + (size_t)row * Dv + d);
+    float fa[8], fb[8];
+    a.unpack(fa); b2.unpack(fb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += fa[j] * fb[j];
+  }
+  s = warp_reduce(s, SumOp());
+  if (lane == 0) {
+    Delta[row] = s;
+    const float l = L[row], m = M[row];
+    lse2[row] = (l > 0.f) ? (natural_stats ? m * kLog2e : m) + log2f(l) : INFINITY;
+  }
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int BH) {
+  auto fn = encode_fn();
+  TYLO_REQUIRE(fn, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)BT, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TYLO_REQUIRE(r == CUDA_SUCCESS, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TYLO_OK;
+}
+
+template <typename T, int D>
+static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V, const void* O,
+                      const void* dO, const float* M, const float* L, float* Delta, float* lse2, const AttnParams& p,
+                      cudaStream_t st) {
+  const long long rows = (long long)p.Sq * p.H * p.B;
+  bwd_prep_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(Delta, lse2, (const T*)O, (const T*)dO, M, L, rows, D,
+                                                                 p.natural_stats);
+  if (int32_t rc = check_launch("attn_bwd_prep")) return rc;
+  CUtensorMap mq, mk, mv, mdo;
+  if (int32_t rc = make_tmap(&mq, Q, D, p.Sq, p.H * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mk, K, D, p.Sk, p.Hkv * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mv, V, D, p.Sk, p.Hkv * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mdo, dO, D, p.Sq, p.H * p.B)) return rc;
+  {
+    auto kern = attn_bwd_sm100_kernel<T, D, DKDV>;
+    TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
+    const long long grid = (long long)((p.Sk + BT - 1) / BT) * p.Hkv * p.B;
+    kern<<<(unsigned)grid, kThreads, Smem<D>::kDynamic, st>>>(mq, mk, mv, mdo, (T*)dV, (T*)dK, lse2, Delta, p);
+    if (int32_t rc = check_launch("attn_bwd_sm100<dkdv>")) return rc;
+  }
+  {
+    auto kern = attn_bwd_sm100_kernel<T, D, DQ>;
+    TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
+    const long long grid = (long long)((p.Sq + BT - 1) / BT) * p.H * p.B;
+    kern<<<(unsigned)grid, kThreads, Smem<D>::kDynamic, st>>>(mq, mk, mv, mdo, (T*)dQ, nullptr, lse2, Delta, p);
+    if (int32_t rc = check_launch("attn_bwd_sm100<dq>")) return rc;
+  }
+  return TYLO_OK;
+}
+
+}  // namespace bwd
+
+bool attn_bwd_sm100_supported(const AttnParams& p, int32_t dtype) {
+  if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
+  if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
+  if (p.k_lengths || p.q_lengths) return false;   // ragged per-batch lengths: generic kernels
+  if (p.d_slopes) return false;                   // score-mod parameter gradients: generic kernels
+  if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2 || (long long)p.Sk * p.Hkv * p.B > 0x7fffffffLL / 2) return false;
+  return true;
+}
+
+int64_t attn_bwd_sm100_workspace_bytes(int Sq, int H, int B) {
+  const int64_t n = (int64_t)Sq * H * B * 4;
+  return (n + 255) / 256 * 256;
+}
+
+int32_t attn_bwd_sm100(void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V, const void* O,
+                       const void* dO, const float* M, const float* L, float* Delta, void* workspace,
+                       const AttnParams& p, int32_t dtype, cudaStream_t st) {
+  float* lse2 = static_cast<float*>(workspace);
+  if (dtype == TYLO_BF16) {
+    if (p.Dk == 128) return bwd::launch<__nv_bfloat16, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+    return bwd::launch<__nv_bfloat16, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+  }
+  if (p.Dk == 128) return bwd::launch<__half, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+  return bwd::launch<__half, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+}
+
+int32_t attn_bwd_sm100_status(int* out) {
+  int v = 0;
+  TYLO_CUDA_OK(cudaMemcpyFromSymbol(&v, g_attn_bwd_status, sizeof(int)));
+  *out = v;
+  if (v != 0) {
+    const int zero = 0;
+    TYLO_CUDA_OK(cudaMemcpyToSymbol(g_attn_bwd_status, &zero, sizeof(int)));
+  }
+  return TYLO_OK;
+}
+
+}  // namespace tylo

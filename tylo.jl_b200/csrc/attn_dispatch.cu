@@ -23,11 +23,19 @@ int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, 
   return TYLO_OK;
 }
 
-int64_t attn_bwd_workspace_bytes(int, int, int, int, int, int, int, int32_t) { return 0; }
+// The workspace is sized for the tensor-core path whenever the dtype and head dim could take it
+// (whether a given call does also depends on its optional arguments).
+int64_t attn_bwd_workspace_bytes(int Dk, int Dv, int Sq, int, int H, int, int B, int32_t dtype) {
+  if ((dtype == TYLO_BF16 || dtype == TYLO_F16) && Dk == Dv && (Dk == 64 || Dk == 128))
+    return attn_bwd_sm100_workspace_bytes(Sq, H, B);
+  return 0;
+}
 
 int32_t attn_bwd_dispatch(void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V,
                           const void* O, const void* dO, const float* M, const float* L, float* Delta,
-                          void* /*workspace*/, const AttnParams& p, int32_t dtype, cudaStream_t st) {
+                          void* workspace, const AttnParams& p, int32_t dtype, cudaStream_t st) {
+  if (!force_generic() && attn_bwd_sm100_supported(p, dtype))
+    return attn_bwd_sm100(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, workspace, p, dtype, st);
   TYLO_DISPATCH_DTYPE(dtype, T, return attn_bwd_generic<T>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, p, st));
   return TYLO_OK;
 }

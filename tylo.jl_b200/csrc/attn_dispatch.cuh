@@ -19,6 +19,15 @@ bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype);
 int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                        const AttnParams& p, int32_t dtype, cudaStream_t st);
 
+// tcgen05 / TMEM / TMA backward for 16-bit storage (attn_bwd_sm100.cu); `workspace` holds one fp32
+// per (query, head, batch): the log2-domain log-sum-exp derived from the saved (M, L).
+bool attn_bwd_sm100_supported(const AttnParams& p, int32_t dtype);
+int64_t attn_bwd_sm100_workspace_bytes(int Sq, int H, int B);
+int32_t attn_bwd_sm100(void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V, const void* O,
+                       const void* dO, const float* M, const float* L, float* Delta, void* workspace,
+                       const AttnParams& p, int32_t dtype, cudaStream_t st);
+int32_t attn_bwd_sm100_status(int* out);
+
 // Reads and clears the device-side status word of the tcgen05 kernels (0 = no bounded wait gave up).
 int32_t attn_fwd_sm100_status(int* out);
 
