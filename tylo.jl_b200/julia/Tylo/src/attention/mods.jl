@@ -1,0 +1,204 @@
+export FullMask, CausalMask, SlidingWindowMask, PrefixMask, DocumentMask
+export AndMask, OrMask, prefix_lm
+export NoOpScore, SoftCapScore, AliBiScore, BiasScore, ComposeScore
+export hmask, hscore
+export grad_shadow
+
+# Score / mask mods.  The types, constructors and operators are the API; the device side is a set of
+# compiled variants inside libtylo_b200 selected through two plain descriptors.  Calling a mod with
+# scalars evaluates it on the host (the CPU reference for the exact mod the kernel runs).
+# Positions are 0-based and absolute (queries are shifted by `input_pos`); `b`, `h` are 1-based.
+
+abstract type MaskMod end
+abstract type ScoreMod end
+
+"Evaluate a mask mod on the host at scalar positions."
+hmask(m::MaskMod, q, kv; b = 1, h = 1) = m(Int32(b), Int32(h), q, kv)
+"Evaluate a score mod on the host for scalar score `s`."
+hscore(m::ScoreMod, s, q, kv; b = 1, h = 1) = m(s, Int32(b), Int32(h), q, kv)
+
+"No masking."
+struct FullMask <: MaskMod end
+(::FullMask)(b, h, q, kv) = true
+
+"`q ≥ kv`."
+struct CausalMask <: MaskMod end
+(::CausalMask)(b, h, q, kv) = q >= kv
+
+"Causal attention within a window: `q - w ≤ kv ≤ q`."
+struct SlidingWindowMask <: MaskMod
+    w::Int32
+end
+(m::SlidingWindowMask)(b, h, q, kv) = (q >= kv) & (q <= kv + m.w)
+
+"Keys at `kv < len` are visible."
+struct PrefixMask <: MaskMod
+    len::Int32
+end
+(m::PrefixMask)(b, h, q, kv) = kv < m.len
+
+"""
+    DocumentMask(doc)            # one Int32 id per absolute position, shared by every batch entry
+    DocumentMask(doc_q, doc_kv)
+
+A pair attends iff its document ids match.  Extension over the reference: an `(S, B)` matrix
+gives every batch entry its own id table.
+"""
+struct DocumentMask{A,B} <: MaskMod
+    doc_q::A
+    doc_kv::B
+end
+DocumentMask(doc::AbstractVecOrMat) = DocumentMask(doc, doc)
+(m::DocumentMask)(b, h, q, kv) = ndims(m.doc_q) == 2 ? m.doc_q[q+1, b] == m.doc_kv[kv+1, b] : m.doc_q[q+1] == m.doc_kv[kv+1]
+
+struct AndMask{A<:MaskMod,B<:MaskMod} <: MaskMod
+    a::A
+    b::B
+end
+(m::AndMask)(b, h, q, kv) = m.a(b, h, q, kv) & m.b(b, h, q, kv)
+
+struct OrMask{A<:MaskMod,B<:MaskMod} <: MaskMod
+    a::A
+    b::B
+end
+(m::OrMask)(b, h, q, kv) = m.a(b, h, q, kv) | m.b(b, h, q, kv)
+
+Base.:&(a::MaskMod, b::MaskMod) = AndMask(a, b)
+Base.:|(a::MaskMod, b::MaskMod) = OrMask(a, b)
+
+"Bidirectional over the first `len` positions, causal after."
+prefix_lm(len) = CausalMask() | PrefixMask(Int32(len))
+
+struct NoOpScore <: ScoreMod end
+(::NoOpScore)(s, b, h, q, kv) = s
+
+"`s -> cap * tanh(s / cap)`."
+struct SoftCapScore <: ScoreMod
+    cap::Float32
+end
+(m::SoftCapScore)(s, b, h, q, kv) = m.cap * tanh(s / m.cap)
+
+"`s + slopes[h] * (q - kv)`, one slope per query head."
+struct AliBiScore{A} <: ScoreMod
+    slopes::A
+end
+(m::AliBiScore)(s, b, h, q, kv) = s + m.slopes[h] * Float32(q - kv)
+
+"Additive bias `(N_kv, M_q, heads, batch)`.  Host evaluation only: libtylo_b200 has no kernel for it."
+struct BiasScore{A} <: ScoreMod
+    bias::A
+    nheads::Int32
+    nbatch::Int32
+end
+BiasScore(bias::AbstractArray{<:Any,4}) = BiasScore(bias, Int32(size(bias, 3)), Int32(size(bias, 4)))
+(m::BiasScore)(s, b, h, q, kv) = s + m.bias[kv+1, q+1, mod1(h, m.nheads), mod1(b, m.nbatch)]
+
+"Apply `a`, then `b`; written `b ∘ a`."
+struct ComposeScore{A<:ScoreMod,B<:ScoreMod} <: ScoreMod
+    a::A
+    b::B
+end
+(m::ComposeScore)(s, b, h, q, kv) = m.b(m.a(s, b, h, q, kv), b, h, q, kv)
+Base.:∘(b::ScoreMod, a::ScoreMod) = ComposeScore(a, b)
+
+"""
+    grad_shadow(x)
+
+Zeroed gradient accumulator: a zeroed copy of an array, or a score mod rebuilt with zeroed array
+fields.  Pass a score-mod shadow as `∂score_mod` to `∇flex_attention!`; valid for one backward call.
+"""
+grad_shadow(x::AbstractArray) = fill!(similar(x), 0)
+grad_shadow(m::AliBiScore) = AliBiScore(grad_shadow(m.slopes))
+grad_shadow(m::ComposeScore) = ComposeScore(grad_shadow(m.a), grad_shadow(m.b))
+grad_shadow(x) = x
+
+# ---- descriptors handed to the library (layout of tylo_mask_desc / tylo_score_desc) -----------------
+const MASK_CAUSAL = UInt32(1); const MASK_SLIDING = UInt32(2); const MASK_DOCUMENT = UInt32(4)
+const MASK_PREFIX = UInt32(8); const MASK_PREFIX_LM = UInt32(16)
+const SCORE_ALIBI = UInt32(1); const SCORE_SOFTCAP = UInt32(2); const SCORE_SOFTCAP_FIRST = UInt32(4)
+
+mutable struct MaskDesc
+    flags::UInt32
+    window::Int32
+    prefix_len::Int32
+    reserved::Int32
+    doc_q::Ptr{Cvoid}
+    doc_kv::Ptr{Cvoid}
+    doc_batch_stride::Int64
+    doc_q_len::Int64
+    doc_kv_len::Int64
+end
+MaskDesc() = MaskDesc(0, 0, 0, 0, C_NULL, C_NULL, 0, 0, 0)
+
+mutable struct ScoreDesc
+    flags::UInt32
+    cap::Float32
+    slopes::Ptr{Cvoid}
+    d_slopes::Ptr{Cvoid}
+end
+ScoreDesc() = ScoreDesc(0, 1.0f0, C_NULL, C_NULL)
+
+unsupported(what) = throw(ArgumentError("$what is unsupported by libtylo_b200 (there is no fallback)"))
+
+describe!(d::MaskDesc, ::FullMask) = d
+describe!(d::MaskDesc, ::CausalMask) = (d.flags |= MASK_CAUSAL; d)
+function describe!(d::MaskDesc, m::SlidingWindowMask)
+    d.window = (d.flags & MASK_SLIDING) != 0 ? min(d.window, m.w) : m.w
+    d.flags |= MASK_SLIDING
+    d
+end
+function describe!(d::MaskDesc, m::PrefixMask)
+    (d.flags & MASK_PREFIX_LM) != 0 && unsupported("PrefixMask combined with prefix_lm")
+    d.prefix_len = (d.flags & MASK_PREFIX) != 0 ? min(d.prefix_len, m.len) : m.len
+    d.flags |= MASK_PREFIX
+    d
+end
+function describe!(d::MaskDesc, m::DocumentMask)
+    (d.flags & MASK_DOCUMENT) != 0 && unsupported("more than one DocumentMask")
+    eltype(m.doc_q) === Int32 && eltype(m.doc_kv) === Int32 || throw(ArgumentError("DocumentMask ids must be Int32"))
+    require_dense(m.doc_q, m.doc_kv)
+    ndims(m.doc_q) == ndims(m.doc_kv) || throw(ArgumentError("doc_q and doc_kv must both be vectors or both matrices"))
+    d.flags |= MASK_DOCUMENT
+    d.doc_q = devptr(m.doc_q); d.doc_kv = devptr(m.doc_kv)
+    d.doc_q_len = size(m.doc_q, 1); d.doc_kv_len = size(m.doc_kv, 1)
+    if ndims(m.doc_q) == 2
+        size(m.doc_q) == size(m.doc_kv) || throw(ArgumentError("per-batch id tables must share one size"))
+        d.doc_batch_stride = size(m.doc_q, 1)
+    end
+    d
+end
+describe!(d::MaskDesc, m::AndMask) = (describe!(d, m.a); describe!(d, m.b))
+function describe!(d::MaskDesc, m::OrMask)
+    a, b = m.a, m.b
+    pm = a isa PrefixMask && b isa CausalMask ? a : (b isa PrefixMask && a isa CausalMask ? b : nothing)
+    (pm === nothing || (d.flags & (MASK_PREFIX | MASK_PREFIX_LM)) != 0) && unsupported("OrMask other than prefix_lm")
+    d.flags |= MASK_PREFIX_LM; d.prefix_len = pm.len
+    d
+end
+describe!(::MaskDesc, m::MaskMod) = unsupported("mask mod $(typeof(m))")
+
+flatten(m::ComposeScore, ∂m) = vcat(flatten(m.a, ∂m === nothing ? nothing : ∂m.a), flatten(m.b, ∂m === nothing ? nothing : ∂m.b))
+flatten(::NoOpScore, ∂m) = Tuple{ScoreMod,Any}[]
+flatten(m::ScoreMod, ∂m) = Tuple{ScoreMod,Any}[(m, ∂m)]
+
+function describe(score_mod::ScoreMod, ∂score_mod = nothing)
+    d = ScoreDesc()
+    chain = flatten(score_mod, ∂score_mod)
+    for (i, (m, ∂m)) in enumerate(chain)
+        if m isa SoftCapScore
+            (d.flags & SCORE_SOFTCAP) != 0 && unsupported("more than one SoftCapScore")
+            d.flags |= SCORE_SOFTCAP; d.cap = m.cap
+            if (d.flags & SCORE_ALIBI) == 0 && any(x -> x[1] isa AliBiScore, chain[i+1:end])
+                d.flags |= SCORE_SOFTCAP_FIRST
+            end
+        elseif m isa AliBiScore
+            (d.flags & SCORE_ALIBI) != 0 && unsupported("more than one AliBiScore")
+            eltype(m.slopes) === Float32 || throw(ArgumentError("AliBiScore slopes must be Float32"))
+            d.flags |= SCORE_ALIBI; d.slopes = devptr(m.slopes)
+            ∂m === nothing || (d.d_slopes = devptr(∂m.slopes))
+        else
+            unsupported("score mod $(typeof(m))")
+        end
+    end
+    d
+end

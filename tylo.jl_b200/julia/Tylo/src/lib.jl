@@ -1,0 +1,43 @@
+# ccall plumbing shared by every wrapper.
+
+const libtylo = get(ENV, "TYLO_B200_LIB", "libtylo_b200")
+
+const BFloat16 = CUDACore.BFloat16
+
+tylo_dtype(::Type{Float32}) = Int32(0)
+tylo_dtype(::Type{BFloat16}) = Int32(1)
+tylo_dtype(::Type{Float16}) = Int32(2)
+tylo_dtype(T::Type) = throw(ArgumentError("libtylo_b200 has no kernels for element type $T"))
+
+# ---- the three version-dependent spellings -------------------------------------------------
+"Raw device pointer of a dense device array (`C_NULL` for `nothing`)."
+devptr(::Nothing) = Ptr{Cvoid}(C_NULL)
+devptr(a) = reinterpret(Ptr{Cvoid}, UInt(pointer(a)))
+"Handle of the CUDA stream of the current task."
+current_stream() = reinterpret(Ptr{Cvoid}, CUDACore.stream().handle)
+"Whether `a` is a dense column-major array (views with gaps are not accepted)."
+is_dense(a) = stride(a, 1) == 1 && all(stride(a, i + 1) == stride(a, i) * size(a, i) for i in 1:ndims(a)-1)
+# ---------------------------------------------------------------------------------------------
+
+function require_dense(arrays...)
+    for a in arrays
+        a === nothing && continue
+        is_dense(a) || throw(ArgumentError("libtylo_b200 takes dense column-major arrays"))
+    end
+end
+
+"Turn a library status into the exception the reference wrapper would have thrown."
+function check(status::Int32)
+    status == 0 && return nothing
+    msg = unsafe_string(ccall((:tylo_b200_last_error, libtylo), Cstring, ()))
+    status == 1 && throw(AssertionError(msg))        # the wrappers' @assert
+    status == 2 && throw(ArgumentError(msg))         # unsupported by libtylo_b200 (no fallback)
+    error("libtylo_b200 status $status: $msg")
+end
+
+"Synchronise and report whether a bounded device-side wait gave up (0 = healthy)."
+function device_status()
+    code = Ref{Int32}(0)
+    check(ccall((:tylo_b200_device_status, libtylo), Int32, (Ref{Int32},), code))
+    return code[]
+end
