@@ -21,6 +21,7 @@
 // P uses the forward's saved statistics through lse2 = log2-domain log-sum-exp, so the element work
 // has no reductions: p = exp2(t - lse2), ds = p (dp - Delta).
 //
+// U (16-bit, two values per column) of column half w overwrites T columns [64w, 64w+32).
 // TMEM columns: [0,128) T1/U1, [128,256) T2/U2, [256,256+D) acc1 (dV), [384,384+D) acc2 (dK or dQ).
 // No multicast, no clusters; every wait is bounded (see sm100_ptx.cuh).
 #include <cuda.h>
@@ -33,6 +34,19 @@ namespace tylo {
 using namespace sm100;
 
 __device__ int g_attn_bwd_status = 0;
+
+// Development aid, compiled only with -DTYLO_BWD_TRACE: clock64 stamps of one CTA's hand-offs.
+#ifdef TYLO_BWD_TRACE
+__device__ long long g_bwd_trace[2 * 2 * 64 * 8];
+__device__ int g_bwd_trace_cta = 0;
+#define TYLO_BTRACE(mode, role, it, ev)                                                                    \
+  do {                                                                                                     \
+    if ((int)blockIdx.x == g_bwd_trace_cta && (it) < 64)                                                   \
+      g_bwd_trace[(((mode) * 2 + (role)) * 64 + (it)) * 8 + (ev)] = clock64();                              \
+  } while (0)
+#else
+#define TYLO_BTRACE(mode, role, it, ev) do {} while (0)
+#endif
 
 namespace bwd {
 
@@ -49,7 +63,7 @@ template <int D> struct Smem {
   static constexpr int kStatStage = 3 * BT * 4;
   static constexpr int kBars = kStats + kStages * kStatStage;
   static constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + kStages, STAT_FULL = Y_EMPTY + kStages,
-                       T_FULL = STAT_FULL + kStages, T_READ = T_FULL + 1, U_FULL = T_READ + 1, DONE = U_FULL + 1,
+                       T_FULL = STAT_FULL + kStages, U_FULL = T_FULL + 1, DONE = U_FULL + 1,
                        kNumBars = DONE + 1;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
@@ -93,6 +107,14 @@ __device__ __forceinline__ void tmem_st32x(uint32_t taddr, const uint32_t* r) {
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 
@@ -172,7 +194,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(SM::Y_FULL + s), 1); mbar_init(bar(SM::Y_EMPTY + s), 1); mbar_init(bar(SM::STAT_FULL + s), 32);
     }
-    mbar_init(bar(SM::T_FULL), 1); mbar_init(bar(SM::T_READ), 256); mbar_init(bar(SM::U_FULL), 256);
+    mbar_init(bar(SM::T_FULL), 1); mbar_init(bar(SM::U_FULL), 256);
     mbar_init(bar(SM::DONE), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -269,11 +291,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (MODE == DKDV) {
 #pragma unroll
           for (int k = 0; k < BT / 16; ++k)
-            mma_ts(tmem + 256, tmem + k * 8, b2 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
+            mma_ts(tmem + 256, tmem + (k / 4) * 64 + (k % 4) * 8, b2 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
         }
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k)
-          mma_ts(tmem + 384, tmem + 128 + k * 8, b1 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
+          mma_ts(tmem + 384, tmem + 128 + (k / 4) * 64 + (k % 4) * 8, b1 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
         tc_commit(bar(SM::Y_EMPTY + (n % kStages)));
       };
       bool ok = mbar_wait(bar(SM::X_FULL), 0, abort_flag, &g_attn_bwd_status, 201);
@@ -282,13 +304,17 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       for (int n = 0; n < n_iter && ok; ++n) {
         ok = mbar_wait(bar(SM::U_FULL), n & 1, abort_flag, &g_attn_bwd_status, 203);
         if (!ok) break;
+        TYLO_BTRACE(MODE, 0, n, 0);
         tc_fence_after();
         issue_acc(n);
+        TYLO_BTRACE(MODE, 0, n, 1);
         if (n + 1 < n_iter) {
           ok = mbar_wait(bar(SM::Y_FULL + (n + 1) % kStages), ((n + 1) / kStages) & 1, abort_flag, &g_attn_bwd_status, 204);
           if (!ok) break;
+          TYLO_BTRACE(MODE, 0, n, 2);
           tc_fence_after();
           issue_t(n + 1);
+          TYLO_BTRACE(MODE, 0, n, 3);
         }
       }
       tc_commit(bar(SM::DONE));
@@ -334,51 +360,65 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
       ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
       if (!ok) break;
+      const bool tracer = (r == 0 && wg == 0);
+      if (tracer) TYLO_BTRACE(MODE, 1, n, 0);
       tc_fence_after();
       uint32_t sv[2][32], dv[2][32];
       tmem_ld32(tmem + lane_off + 64 * wg, sv[0]); tmem_ld32(tmem + lane_off + 64 * wg + 32, sv[1]);
       tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
       tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(SM::T_READ));
+      if (tracer) TYLO_BTRACE(MODE, 1, n, 1);
 
       const float* slse = stat(s, 0); const float* sdel = stat(s, 1); const int* sdoc = reinterpret_cast<const int*>(stat(s, 2));
-      uint32_t up[32], ud[32];
       auto run = [&](auto modded_c, auto partial_c) {
         constexpr bool MOD = decltype(modded_c)::value, PART = decltype(partial_c)::value;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
+          uint32_t up[16], ud[16];    // 32 columns at a time keeps the live register set small
 #pragma unroll
-          for (int t = 0; t < 32; t += 2) {
-            float pp[2], dd[2];
+          for (int t = 0; t < 32; t += 4) {
+            const int col0 = 64 * wg + q * 32 + t;
+            float lse4[4], del4[4];
+            int doc4[4] = {0, 0, 0, 0};
+            if (MODE == DKDV) {
+              *reinterpret_cast<float4*>(lse4) = *reinterpret_cast<const float4*>(slse + col0);
+              *reinterpret_cast<float4*>(del4) = *reinterpret_cast<const float4*>(sdel + col0);
+            }
+            if (PART) *reinterpret_cast<int4*>(doc4) = *reinterpret_cast<const int4*>(sdoc + col0);
+            float pp[4], dd[4];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = 64 * wg + q * 32 + t + e;
+            for (int e = 0; e < 4; ++e) {
+              const int col = col0 + e;
               const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
               const int kv = (MODE == DKDV) ? own_row : tile0 + col;
-              const float lse = (MODE == DKDV) ? slse[col] : my_lse;
-              const float del = (MODE == DKDV) ? sdel[col] : my_delta;
-              const int dq = (MODE == DKDV) ? (PART ? sdoc[col] : 0) : my_doc;
-              const int dk = (MODE == DKDV) ? my_doc : (PART ? sdoc[col] : 0);
+              const float lse = (MODE == DKDV) ? lse4[e] : my_lse;
+              const float del = (MODE == DKDV) ? del4[e] : my_delta;
+              const int dq = (MODE == DKDV) ? doc4[e] : my_doc;
+              const int dk = (MODE == DKDV) ? my_doc : doc4[e];
               pp[e] = element<MOD, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
                                          lse, del, qpos, kv, row_ok, dq, dk, dd[e]);
             }
-            up[q * 16 + t / 2] = pack16<T>(pp[0], pp[1]);
-            ud[q * 16 + t / 2] = pack16<T>(dd[0], dd[1]);
+            up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
+            ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
           }
+          // this warpgroup's packed columns overwrite the first half of its own T columns (all of which
+          // are already in registers)
+          if (MODE == DKDV) tmem_st16x(tmem + lane_off + 64 * wg + q * 16, up);
+          tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
         }
       };
       if (modded) { if (partial) run(std::true_type{}, std::true_type{}); else run(std::true_type{}, std::false_type{}); }
       else { if (partial) run(std::false_type{}, std::true_type{}); else run(std::false_type{}, std::false_type{}); }
 
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T_READ), n & 1, abort_flag, &g_attn_bwd_status, 303));
-      if (!ok) break;
-      tc_fence_after();
-      if (MODE == DKDV) tmem_st32x(tmem + lane_off + 32 * wg, up);
-      tmem_st32x(tmem + 128 + lane_off + 32 * wg, ud);
+      if (tracer) TYLO_BTRACE(MODE, 1, n, 2);
+      // Each warpgroup writes its 32 packed columns over the first half of ITS OWN 64 T columns (the
+      // MMA addresses the two 32-column pieces separately), so no thread overwrites T values that
+      // another thread has yet to read and the two warpgroups need no rendezvous here.
+      if (tracer) TYLO_BTRACE(MODE, 1, n, 3);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(SM::U_FULL));
+      if (tracer) TYLO_BTRACE(MODE, 1, n, 4);
     }
 
     // ---- epilogue: this warpgroup stores columns [wg*D/2, (wg+1)*D/2) of each accumulator
@@ -533,6 +573,15 @@ int32_t attn_bwd_sm100(void* dQ, void* dK, void* dV, const void* Q, const void* 
   if (p.Dk == 128) return bwd::launch<__half, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
   return bwd::launch<__half, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
 }
+
+#ifdef TYLO_BWD_TRACE
+extern "C" int32_t tylo_b200_debug_bwd_trace(long long* out, int cta) {
+  cudaDeviceSynchronize();
+  if (out) cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * 2 * 2 * 64 * 8);
+  cudaMemcpyToSymbol(g_bwd_trace_cta, &cta, sizeof(int));
+  return 0;
+}
+#endif
 
 int32_t attn_bwd_sm100_status(int* out) {
   int v = 0;
