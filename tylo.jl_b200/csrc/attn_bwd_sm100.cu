@@ -63,7 +63,7 @@ template <int D> struct Smem {
   static constexpr int kStatStage = 3 * BT * 4;
   static constexpr int kBars = kStats + kStages * kStatStage;
   static constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + kStages, STAT_FULL = Y_EMPTY + kStages,
-                       T_FULL = STAT_FULL + kStages, U_FULL = T_FULL + 1, DONE = U_FULL + 1,
+                       T1_FULL = STAT_FULL + kStages, T2_FULL = T1_FULL + 1, U1_FULL = T2_FULL + 1, U2_FULL = U1_FULL + 1, DONE = U2_FULL + 1,
                        kNumBars = DONE + 1;
   static constexpr int kMisc = kBars + 8 * kNumBars;
   static constexpr int kTotal = kMisc + 16;
@@ -110,6 +110,14 @@ __device__ __forceinline__ void tmem_st32x(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// 16-byte shared-memory load into four registers (explicit shared-space address: no generic
+// addressing, no array the compiler would have to keep in local memory)
+__device__ __forceinline__ void lds128(uint32_t saddr, float& a, float& b, float& c, float& d) {
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(saddr));
+}
+__device__ __forceinline__ void lds128i(uint32_t saddr, int& a, int& b, int& c, int& d) {
+  asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(saddr));
+}
 __device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -173,7 +181,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   int it_lo, it_n, n_iter;   // streamed tile range [it_lo, it_lo + it_n) per head; n_iter over the group
   if (MODE == DKDV) {
     const int nkt = (p.Sk + BT - 1) / BT;
-    const int kt = blockIdx.x % nkt, hkb = blockIdx.x / nkt;
+    const int nhkb = p.Hkv * p.B;
+    const int kt = blockIdx.x / nhkb, hkb = blockIdx.x % nhkb;   // key tile slowest: under a causal mask the
+    (void)nkt;                                                    // low tiles carry the most work and start first
     b = hkb / p.Hkv; hk = hkb % p.Hkv; h0 = hk * p.G; own0 = kt * BT;
     int lo, hi;
     q_range(p, own0, min(own0 + BT, p.Sk) - 1, p.Sq, &lo, &hi);
@@ -194,7 +204,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(SM::Y_FULL + s), 1); mbar_init(bar(SM::Y_EMPTY + s), 1); mbar_init(bar(SM::STAT_FULL + s), 32);
     }
-    mbar_init(bar(SM::T_FULL), 1); mbar_init(bar(SM::U_FULL), 256);
+    mbar_init(bar(SM::T1_FULL), 1); mbar_init(bar(SM::T2_FULL), 1);
+    mbar_init(bar(SM::U1_FULL), 256); mbar_init(bar(SM::U2_FULL), 256);
     mbar_init(bar(SM::DONE), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -270,29 +281,36 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint64_t dmn_hi = smem_desc_sw128(0, BT * 128, 1024);     // MN-major operand
       auto desc_at = [](uint64_t hi, uint32_t saddr) { return hi | (uint64_t)((saddr & 0x3ffff) >> 4); };
       const uint32_t x1 = sbase + SM::kX, x2 = x1 + SM::kTile;
-      auto issue_t = [&](int n) {
-        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile, y2 = y1 + SM::kTile;
-        const uint64_t a1 = desc_at(dk_hi, x1), a2 = desc_at(dk_hi, x2), b1 = desc_at(dk_hi, y1), b2 = desc_at(dk_hi, y2);
+      auto issue_t1 = [&](int n) {     // T1 = X1 Y1^T  (S^T or S)
+        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile;
+        const uint64_t a1 = desc_at(dk_hi, x1), b1 = desc_at(dk_hi, y1);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = ((k / 4) * (BT * 128) + (k % 4) * 32) >> 4;
           mma_ss(tmem, a1 + off, b1 + off, idesc_ss, k > 0);
         }
+        tc_commit(bar(SM::T1_FULL));
+      };
+      auto issue_t2 = [&](int n) {     // T2 = X2 Y2^T  (dP^T or dP)
+        const uint32_t y2 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile + SM::kTile;
+        const uint64_t a2 = desc_at(dk_hi, x2), b2 = desc_at(dk_hi, y2);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = ((k / 4) * (BT * 128) + (k % 4) * 32) >> 4;
           mma_ss(tmem + 128, a2 + off, b2 + off, idesc_ss, k > 0);
         }
-        tc_commit(bar(SM::T_FULL));
+        tc_commit(bar(SM::T2_FULL));
       };
-      auto issue_acc = [&](int n) {
-        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile, y2 = y1 + SM::kTile;
-        const uint64_t b1 = desc_at(dmn_hi, y1), b2 = desc_at(dmn_hi, y2);
-        if (MODE == DKDV) {
+      auto issue_acc1 = [&](int n) {   // dV += P^T dO (DKDV only)
+        const uint32_t y2 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile + SM::kTile;
+        const uint64_t b2 = desc_at(dmn_hi, y2);
 #pragma unroll
-          for (int k = 0; k < BT / 16; ++k)
-            mma_ts(tmem + 256, tmem + (k / 4) * 64 + (k % 4) * 8, b2 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
-        }
+        for (int k = 0; k < BT / 16; ++k)
+          mma_ts(tmem + 256, tmem + (k / 4) * 64 + (k % 4) * 8, b2 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
+      };
+      auto issue_acc2 = [&](int n) {   // dK += dS^T Q  /  dQ += dS K
+        const uint32_t y1 = sbase + SM::kY + (n % kStages) * 2 * SM::kTile;
+        const uint64_t b1 = desc_at(dmn_hi, y1);
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k)
           mma_ts(tmem + 384, tmem + 128 + (k / 4) * 64 + (k % 4) * 8, b1 + (uint32_t)((k * 2048) >> 4), idesc_ts, (n > 0) || (k > 0));
@@ -300,22 +318,28 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       };
       bool ok = mbar_wait(bar(SM::X_FULL), 0, abort_flag, &g_attn_bwd_status, 201);
       ok = ok && mbar_wait(bar(SM::Y_FULL + 0), 0, abort_flag, &g_attn_bwd_status, 202);
-      if (ok) { tc_fence_after(); issue_t(0); }
+      if (ok) { tc_fence_after(); issue_t1(0); issue_t2(0); }
+      // Issue order per streamed tile n:  [U1(n) ready] acc1(n), T1(n+1)   [U2(n) ready] acc2(n), T2(n+1).
+      // T1(n+1) only needs the T1 columns released (U1_FULL: P^T stored, or in DQ mode S read), so the
+      // compute warps find the next S waiting when they finish tile n, while acc2(n) and T2(n+1) run.
       for (int n = 0; n < n_iter && ok; ++n) {
-        ok = mbar_wait(bar(SM::U_FULL), n & 1, abort_flag, &g_attn_bwd_status, 203);
+        ok = mbar_wait(bar(SM::U1_FULL), n & 1, abort_flag, &g_attn_bwd_status, 205);
         if (!ok) break;
-        TYLO_BTRACE(MODE, 0, n, 0);
         tc_fence_after();
-        issue_acc(n);
-        TYLO_BTRACE(MODE, 0, n, 1);
+        if (MODE == DKDV) issue_acc1(n);
         if (n + 1 < n_iter) {
           ok = mbar_wait(bar(SM::Y_FULL + (n + 1) % kStages), ((n + 1) / kStages) & 1, abort_flag, &g_attn_bwd_status, 204);
           if (!ok) break;
-          TYLO_BTRACE(MODE, 0, n, 2);
           tc_fence_after();
-          issue_t(n + 1);
-          TYLO_BTRACE(MODE, 0, n, 3);
+          issue_t1(n + 1);
         }
+        ok = mbar_wait(bar(SM::U2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 203);
+        if (!ok) break;
+        TYLO_BTRACE(MODE, 0, n, 0);
+        tc_fence_after();
+        issue_acc2(n);
+        TYLO_BTRACE(MODE, 0, n, 1);
+        if (n + 1 < n_iter) { issue_t2(n + 1); TYLO_BTRACE(MODE, 0, n, 3); }
       }
       tc_commit(bar(SM::DONE));
       mbar_drain(bar(SM::DONE), 0);
@@ -358,66 +382,130 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
 
       ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
-      ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
+      ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T1_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
       if (!ok) break;
       const bool tracer = (r == 0 && wg == 0);
       if (tracer) TYLO_BTRACE(MODE, 1, n, 0);
       tc_fence_after();
       uint32_t sv[2][32], dv[2][32];
       tmem_ld32(tmem + lane_off + 64 * wg, sv[0]); tmem_ld32(tmem + lane_off + 64 * wg + 32, sv[1]);
-      tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
       tc_wait_ld();
       if (tracer) TYLO_BTRACE(MODE, 1, n, 1);
+      const uint32_t stat_u = sbase + SM::kStats + s * SM::kStatStage;   // lse2[128], delta[128], doc[128]
 
-      const float* slse = stat(s, 0); const float* sdel = stat(s, 1); const int* sdoc = reinterpret_cast<const int*>(stat(s, 2));
-      auto run = [&](auto modded_c, auto partial_c) {
-        constexpr bool MOD = decltype(modded_c)::value, PART = decltype(partial_c)::value;
+      // Each warpgroup writes its packed 16-bit columns over the first half of ITS OWN 64 T columns
+      // (the MMA addresses the two 32-column pieces separately), so no thread overwrites T values
+      // another thread has yet to read and the two warpgroups need no rendezvous.
+      if (!modded) {
+        // pass 1 (while the dP MMAs run): p = exp2(c s - lse2), masked; kept in fp32 over sv
+        auto pass_p = [&](auto partial_c) {
+          constexpr bool PART = decltype(partial_c)::value;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            uint32_t up[16];
+#pragma unroll
+            for (int t = 0; t < 32; t += 4) {
+              const int col0 = 64 * wg + q * 32 + t;
+              float l0 = my_lse, l1 = my_lse, l2 = my_lse, l3 = my_lse;
+              int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+              if (MODE == DKDV) lds128(stat_u + col0 * 4, l0, l1, l2, l3);
+              if (PART) lds128i(stat_u + 2 * BT * 4 + col0 * 4, d0, d1, d2, d3);
+              const float lse4[4] = {l0, l1, l2, l3};
+              const int doc4[4] = {d0, d1, d2, d3};
+              float pp[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int col = col0 + e;
+                const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
+                const int kv = (MODE == DKDV) ? own_row : tile0 + col;
+                float unused;
+                pp[e] = element<false, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), 0.f, lse4[e], 0.f, qpos, kv,
+                                             row_ok, (MODE == DKDV) ? doc4[e] : my_doc, (MODE == DKDV) ? my_doc : doc4[e], unused);
+                sv[q][t + e] = __float_as_uint(pp[e]);
+              }
+              up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
+            }
+            if (MODE == DKDV) tmem_st16x(tmem + lane_off + 64 * wg + q * 16, up);
+          }
+        };
+        if (partial) pass_p(std::true_type{}); else pass_p(std::false_type{});
+        if (MODE == DKDV) tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(SM::U1_FULL));       // T1 columns released: dV's MMAs / the next S may start
+        if (tracer) TYLO_BTRACE(MODE, 1, n, 2);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 303));
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
+        tc_wait_ld();
+        if (tracer) TYLO_BTRACE(MODE, 1, n, 3);
+        // pass 2: ds = p (dp - delta) * scale
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          uint32_t up[16], ud[16];    // 32 columns at a time keeps the live register set small
+          uint32_t ud[16];
 #pragma unroll
           for (int t = 0; t < 32; t += 4) {
             const int col0 = 64 * wg + q * 32 + t;
-            float lse4[4], del4[4];
-            int doc4[4] = {0, 0, 0, 0};
-            if (MODE == DKDV) {
-              *reinterpret_cast<float4*>(lse4) = *reinterpret_cast<const float4*>(slse + col0);
-              *reinterpret_cast<float4*>(del4) = *reinterpret_cast<const float4*>(sdel + col0);
-            }
-            if (PART) *reinterpret_cast<int4*>(doc4) = *reinterpret_cast<const int4*>(sdoc + col0);
-            float pp[4], dd[4];
+            float e0 = my_delta, e1 = my_delta, e2 = my_delta, e3 = my_delta;
+            if (MODE == DKDV) lds128(stat_u + BT * 4 + col0 * 4, e0, e1, e2, e3);
+            const float del4[4] = {e0, e1, e2, e3};
+            float dd[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = col0 + e;
-              const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
-              const int kv = (MODE == DKDV) ? own_row : tile0 + col;
-              const float lse = (MODE == DKDV) ? lse4[e] : my_lse;
-              const float del = (MODE == DKDV) ? del4[e] : my_delta;
-              const int dq = (MODE == DKDV) ? doc4[e] : my_doc;
-              const int dk = (MODE == DKDV) ? my_doc : doc4[e];
-              pp[e] = element<MOD, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
-                                         lse, del, qpos, kv, row_ok, dq, dk, dd[e]);
-            }
-            up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
+            for (int e = 0; e < 4; ++e)
+              dd[e] = __uint_as_float(sv[q][t + e]) * (__uint_as_float(dv[q][t + e]) - del4[e]) * p.scale;
             ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
           }
-          // this warpgroup's packed columns overwrite the first half of its own T columns (all of which
-          // are already in registers)
-          if (MODE == DKDV) tmem_st16x(tmem + lane_off + 64 * wg + q * 16, up);
           tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
         }
-      };
-      if (modded) { if (partial) run(std::true_type{}, std::true_type{}); else run(std::true_type{}, std::false_type{}); }
-      else { if (partial) run(std::false_type{}, std::true_type{}); else run(std::false_type{}, std::false_type{}); }
-
-      if (tracer) TYLO_BTRACE(MODE, 1, n, 2);
-      // Each warpgroup writes its 32 packed columns over the first half of ITS OWN 64 T columns (the
-      // MMA addresses the two 32-column pieces separately), so no thread overwrites T values that
-      // another thread has yet to read and the two warpgroups need no rendezvous here.
-      if (tracer) TYLO_BTRACE(MODE, 1, n, 3);
+      } else {
+        // score mods: p and the VJP factor come out of one evaluation, so both T tiles are awaited first
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 303));
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
+        tc_wait_ld();
+        auto run = [&](auto partial_c) {
+          constexpr bool PART = decltype(partial_c)::value;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            uint32_t up[16], ud[16];
+#pragma unroll
+            for (int t = 0; t < 32; t += 4) {
+              const int col0 = 64 * wg + q * 32 + t;
+              float l0 = my_lse, l1 = my_lse, l2 = my_lse, l3 = my_lse, e0 = my_delta, e1 = my_delta, e2 = my_delta, e3 = my_delta;
+              int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+              if (MODE == DKDV) {
+                lds128(stat_u + col0 * 4, l0, l1, l2, l3);
+                lds128(stat_u + BT * 4 + col0 * 4, e0, e1, e2, e3);
+              }
+              if (PART) lds128i(stat_u + 2 * BT * 4 + col0 * 4, d0, d1, d2, d3);
+              const float lse4[4] = {l0, l1, l2, l3}, del4[4] = {e0, e1, e2, e3};
+              const int doc4[4] = {d0, d1, d2, d3};
+              float pp[4], dd[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int col = col0 + e;
+                const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
+                const int kv = (MODE == DKDV) ? own_row : tile0 + col;
+                pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
+                                            lse4[e], del4[e], qpos, kv, row_ok, (MODE == DKDV) ? doc4[e] : my_doc,
+                                            (MODE == DKDV) ? my_doc : doc4[e], dd[e]);
+              }
+              up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
+              ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
+            }
+            if (MODE == DKDV) tmem_st16x(tmem + lane_off + 64 * wg + q * 16, up);
+            tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
+          }
+        };
+        if (partial) run(std::true_type{}); else run(std::false_type{});
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(SM::U1_FULL));
+      }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(SM::U_FULL));
+      mbar_arrive(bar(SM::U2_FULL));
       if (tracer) TYLO_BTRACE(MODE, 1, n, 4);
     }
 
