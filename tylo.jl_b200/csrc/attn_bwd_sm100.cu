@@ -552,26 +552,29 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 }
 
 // Delta[row] = sum_d dO*O and lse2[row] = log2-domain log-sum-exp from the forward's (M, L).
-template <typename T>
+// LPR = Dv / 8 lanes share a row (one 16-byte packet each), so a warp covers 32 / LPR rows.
+template <typename T, int LPR>
 __global__ void __launch_bounds__(256)
 bwd_prep_kernel(float* __restrict__ Delta, float* __restrict__ lse2, const T* __restrict__ O,
                 const T* __restrict__ dO, const float* __restrict__ M, const float* __restrict__ L,
-                long long rows, int Dv, int natural_stats) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
+                long long rows, int natural_stats) {
+  constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
+  const int sub = lane % LPR;
   float s = 0.f;
-  for (int d = lane * 8; d < Dv; d += 256) {
+  if (row < rows) {
     Pack<T> a, b2;
-    a.raw = *reinterpret_cast<const uint4*>(O + (size_t)row * Dv + d);
-    b2.raw = *reinterpret_cast<const uint4*>(dO + (size_t)row * Dv + d);
+    a.raw = ld_stream(O + (size_t)row * (LPR * 8) + sub * 8);
+    b2.raw = ld_stream(dO + (size_t)row * (LPR * 8) + sub * 8);
     float fa[8], fb[8];
     a.unpack(fa); b2.unpack(fb);
 #pragma unroll
     for (int j = 0; j < 8; ++j) s += fa[j] * fb[j];
   }
-  s = warp_reduce(s, SumOp());
-  if (lane == 0) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (sub == 0 && row < rows) {
     Delta[row] = s;
     const float l = L[row], m = M[row];
     lse2[row] = (l > 0.f) ? (natural_stats ? m * kLog2e : m) + log2f(l) : INFINITY;
@@ -609,8 +612,9 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
                       const void* dO, const float* M, const float* L, float* Delta, float* lse2, const AttnParams& p,
                       cudaStream_t st) {
   const long long rows = (long long)p.Sq * p.H * p.B;
-  bwd_prep_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(Delta, lse2, (const T*)O, (const T*)dO, M, L, rows, D,
-                                                                 p.natural_stats);
+  constexpr int LPR = D / 8, RPB = 8 * (32 / LPR);   // lanes per row, rows per 256-thread block
+  bwd_prep_kernel<T, LPR><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(Delta, lse2, (const T*)O, (const T*)dO, M, L,
+                                                                             rows, p.natural_stats);
   if (int32_t rc = check_launch("attn_bwd_prep")) return rc;
   CUtensorMap mq, mk, mv, mdo;
   if (int32_t rc = make_tmap(&mq, Q, D, p.Sq, p.H * p.B)) return rc;

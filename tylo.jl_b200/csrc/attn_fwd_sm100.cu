@@ -22,6 +22,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <type_traits>
+
 #include "attn_dispatch.cuh"
 #include "sm100_ptx.cuh"
 
@@ -162,7 +164,33 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
 
     // score mods (compile-time selected), then the element-wise mask only on tiles that need it
     // (a warp-uniform branch around the whole pass), then the row max over independent chains
-    if (modded) {
+    bool mods_done = false;
+    if (modded && score_flags == TYLO_SCORE_SOFTCAP) {
+      // Soft cap alone: if every score of the warp's rows is small against the cap (the usual case),
+      // tanh is a branch-free odd polynomial on the FMA pipe for the whole tile.
+      float am[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int t = 0; t < 32; t += 2)
+          am[q] = max3(am[q], fabsf(__uint_as_float(sr[q][t])), fabsf(__uint_as_float(sr[q][t + 1])));
+      }
+      const float k1 = p.scale * inv_cap;
+      if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * k1 < 0.4f)) {
+        const float k2 = p.cap * kLog2e;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            const float x = __uint_as_float(sr[q][t]) * k1, x2 = x * x;
+            const float th = x * fmaf(x2, fmaf(x2, fmaf(x2, -0.05396825f, 0.13333334f), -0.33333334f), 1.f);
+            sr[q][t] = __float_as_uint(th * k2);
+          }
+        }
+        mods_done = true;
+      }
+    }
+    if (modded && !mods_done) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
 #pragma unroll
@@ -178,22 +206,29 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       }
     }
     if (partial) {
+      // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
+      // runtime condition makes the compiler wrap every one of the 128 in a convergence barrier.
+      auto mask_pass = [&](auto with_doc) {
+        constexpr bool DOCS = decltype(with_doc)::value;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          const int kv = kv0 + q * 32 + t;
-          int key_doc = 0;
-          if (doc_elementwise) key_doc = __shfl_sync(0xffffffffu, ids[q], t);   // warp-uniform branch
-          bool keep = (kv < p.Sk) && row_doc_ok;
-          if (mask_flags & TYLO_MASK_CAUSAL) keep = keep && (qpos >= kv);
-          if (mask_flags & TYLO_MASK_SLIDING) keep = keep && (qpos >= kv) && (qpos <= kv + p.window);
-          if (mask_flags & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
-          if (mask_flags & TYLO_MASK_PREFIX_LM) keep = keep && ((qpos >= kv) || (kv < p.prefix_len));
-          if (doc_elementwise) keep = keep && (key_doc == my_doc);
-          if (!keep) sr[q][t] = 0xff800000u;   // -inf
+          for (int t = 0; t < 32; ++t) {
+            const int kv = kv0 + q * 32 + t;
+            bool keep = (kv < p.Sk) && row_doc_ok;
+            if (mask_flags & TYLO_MASK_CAUSAL) keep = keep && (qpos >= kv);
+            if (mask_flags & TYLO_MASK_SLIDING) keep = keep && (qpos >= kv) && (qpos <= kv + p.window);
+            if (mask_flags & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
+            if (mask_flags & TYLO_MASK_PREFIX_LM) keep = keep && ((qpos >= kv) || (kv < p.prefix_len));
+            if (DOCS) {
+              const int key_doc = __shfl_sync(0xffffffffu, ids[q], t);   // every lane takes part, masked or not
+              keep = keep && (key_doc == my_doc);
+            }
+            sr[q][t] = keep ? sr[q][t] : 0xff800000u;   // -inf
+          }
         }
-      }
+      };
+      if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
     }
     float mxq[4][2];
 #pragma unroll
@@ -209,6 +244,18 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
                            fmaxf(mxq[3][0], mxq[3][1]));
     m_true = fmaxf(m_true, mx);
     if (tracer) TYLO_TRACE(1 + X, i, 2);
+    if (__all_sync(0xffffffffu, mx == -INFINITY)) {
+      // every pair of this warp's 32 rows is masked in this tile (e.g. keys of another document):
+      // P = 0, nothing to exponentiate or rescale
+      uint32_t z[32];
+#pragma unroll
+      for (int t = 0; t < 32; ++t) z[t] = 0u;
+      tmem_st32(ts, z); tmem_st32(ts + 32, z);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(SM::P_FULL + X));
+      continue;
+    }
     // lazy rescaling: move the reference max only when it would otherwise overflow the 2^8 headroom
     const bool need = (mx > m_ref) && ((m_ref == -INFINITY) || ((mx - m_ref) * c > 8.f));
     if (__any_sync(0xffffffffu, need)) {
