@@ -11,8 +11,8 @@ softmax in GB/s, backward and flex in TFLOP/s), each with its own roofline fract
 
 Multi-GPU (`--gpus N`, launched under torchrun): prefill shards over batch x heads with no
 communication (every rank runs the per-GPU problem: weak scaling); the 1M-token decode extra
-shards the KV sequence across ranks and merges the per-rank (O, max, sum) partials with an
-NCCL all-gather followed by the library's combine kernel.
+shards the KV sequence across ranks and merges the per-rank (O, max, sum) partials with the
+library's own exchange kernel (peer stores over NVLink into IPC-shared buffers, one launch).
 
 `--impl reference` times the CPU restatement of the reference's plain-array code (the oracle;
 the reference itself is Julia and cannot run here) on the host cores, on a bounded sample.
@@ -228,21 +228,15 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
     kv_bytes = total_len * Hkv * 2 * D * 2                       # live K+V bytes over all ranks
     w = dict(name="decode_1m" if long_ctx else "decode_ragged", unit="GB/s", bound="hbm", scale=1e-9, launches=2)
     if long_ctx and world > 1:
-        n = B * H * D
-        pack = torch.empty(n + 2 * B * H, dtype=torch.float32, device="cuda")
-        merged = t.DecodeScratch(pack[:n].view(1, B, H, D), pack[n:n + B * H].view(1, B, H), pack[n + B * H:].view(1, B, H))
-        gathered = torch.empty(world * pack.numel(), dtype=torch.float32, device="cuda")
-        stride = pack.numel()
+        # Receive buffers shared over CUDA IPC; the merge across GPUs is one launch of the library's own
+        # exchange kernel (peer stores over NVLink + flags), no collective-library call on the data path.
+        ex = t.DecodeExchange(B, H, D, rank=rank, world=world)
+        w["exchange"] = ex
 
         def step():
-            t.decode_split_(Q, K, V, lengths=lengths, scratch=sc)
-            t.decode_combine_(None, sc.O_partial, sc.M_partial, sc.L_partial, n_splits=n_splits, o_stride=n,
-                              ml_stride=B * H, Dv=D, H=H, B=B, merged=merged)
-            dist.all_gather_into_tensor(gathered, pack)
-            t.decode_combine_(O, gathered, gathered[n:], gathered[n + B * H:], n_splits=world, o_stride=stride,
-                              ml_stride=stride, Dv=D, H=H, B=B)
+            t.sharded_decode_attention_(O, Q, K, V, lengths_local=lengths, exchange=ex, scratch=sc)
 
-        # The sharded step is four short launches (~80 us of work per GPU at 8 GPUs): replay it as one
+        # The sharded step is two short launches (~80 us of work per GPU at 8 GPUs): replay it as one
         # CUDA graph so that launch gaps do not dominate.  Falls back to eager launches if capture fails.
         eager = step
         eager(); torch.cuda.synchronize(); dist.barrier()
@@ -255,10 +249,10 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
         except Exception:
             step = eager
             w["graphed"] = False
-        w.update(step=step, work=kv_bytes // world, launches=3, global_work=kv_bytes)
+        w.update(step=step, work=kv_bytes // world, launches=2, global_work=kv_bytes)
     else:
         w.update(step=lambda: t.decode_attention_(O, Q, K, V, lengths=lengths, scratch=sc), work=kv_bytes, global_work=kv_bytes)
-    w["config"] = dict(workload=("split-KV decode, bf16, 1 sequence x 1,048,576 keys" + (f", KV sharded over {world} GPUs + NCCL merge" if world > 1 else ""))
+    w["config"] = dict(workload=("split-KV decode, bf16, 1 sequence x 1,048,576 keys" + (f", KV sharded over {world} GPUs, merged by one peer-store exchange launch over NVLink" if world > 1 else ""))
                        if long_ctx else "split-KV decode, bf16, 64 sequences, lengths U[1024,32768]",
                        heads_q=H, heads_kv=Hkv, head_dim=D, n_splits=n_splits, live_kv_bytes=kv_bytes,
                        cuda_graph=w.get("graphed", False))
@@ -392,6 +386,13 @@ def main():
         if dist is not None:
             dist.barrier()
 
+    def all_ranks_ok(ok):
+        if world == 1:
+            return ok
+        v = torch.tensor([1.0 if ok else 0.0], device="cuda")
+        dist.all_reduce(v, op=dist.ReduceOp.MIN)
+        return bool(v.item() > 0.5)
+
     def max_over_ranks(ms):
         if dist is None:
             return ms
@@ -448,15 +449,29 @@ def main():
             names = [n for n in names if n in args.extras.split(",")]
         extras = {}
         for n in names:
+            w, err = None, None
             try:
                 w = makers[n]()
+            except Exception as e:  # an extra must never take the headline down
+                err = f"{type(e).__name__}: {e}"
+            if not all_ranks_ok(err is None):      # every rank times the extra, or none does
+                extras[n] = {"error": err or "setup failed on another rank"}
+                w = None
+                torch.cuda.empty_cache()
+                continue
+            try:
                 k = max(3, min(args.steps, 10))
                 ems = max_over_ranks(time_steps(torch, w["step"], k, 3, sync_all))
+                if "exchange" in w:
+                    w["exchange"].status()          # raises if a bounded wait for a peer's record gave up
                 r = roofline(w, ems)
                 extras[n] = {"value": replicated(w) * w["scale"] / (ems * 1e-3), "unit": w["unit"], "ms_per_step": ems,
                              "steps": k, "roofline_frac": r["frac"], "per_gpu": r["achieved"], "config": w["config"]}
-            except Exception as e:  # an extra must never take the headline down
+            except Exception as e:
                 extras[n] = {"error": f"{type(e).__name__}: {e}"}
+            if w is not None and "exchange" in w:
+                sync_all()
+                w["exchange"].close()
             w = None
             torch.cuda.empty_cache()
         line["extras"] = extras

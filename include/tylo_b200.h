@@ -223,6 +223,42 @@ int32_t tylo_b200_decode_attention_static(void* O, const void* Q, const void* K,
                                           int32_t dtype, tylo_stream_t stream);
 int64_t tylo_b200_decode_static_scratch_floats(void);
 
+/* ---- decode with the KV cache of a sequence sharded over the GPUs of one node -------------------
+ * No counterpart in the reference, which is single-GPU; the merge algebra is the reference's own
+ * (mha_decode_combine, decode.jl:119-140) applied once more across GPUs.  Each GPU runs
+ * tylo_b200_decode_split on its own key range, then tylo_b200_decode_exchange: ONE launch that
+ * merges the local splits, stores the merged record into every peer's receive buffer over
+ * NVLink (plain peer stores + a release flag per (peer, head)), waits — bounded — for the peers'
+ * records of the same call and writes the final O (Dv,H,B) on every GPU.
+ *
+ * Receive buffers: one per GPU, tylo_b200_decode_exchange_bytes(world, Dv, H, B) bytes, zeroed,
+ * mapped into every process (tylo_b200_peer_* below).  `peer_buffers` is a HOST array of `world`
+ * device pointers, entry r = rank r's buffer as mapped in this process (entry `rank` = own).
+ * All ranks must make the same sequence of calls on a buffer set (a per-head call counter lives
+ * in the buffer); records are double-buffered, so calls may be replayed from a CUDA graph.
+ * `timeout_us` bounds the wait for each peer (<= 0: two seconds).  When it runs out the kernel
+ * leaves O untouched, sets the buffer's status word and returns; the context stays usable and
+ * tylo_b200_decode_exchange_status reports TYLO_ERR_DEVICE_TIMEOUT once (reads and clears). */
+int64_t tylo_b200_decode_exchange_bytes(int32_t world, int32_t Dv, int32_t H, int32_t B);
+int32_t tylo_b200_decode_exchange(void* O, const float* O_partial, const float* M_partial,
+                                  const float* L_partial,
+                                  int32_t n_splits, int64_t o_stride, int64_t ml_stride,
+                                  void* const* peer_buffers, int32_t rank, int32_t world,
+                                  int32_t Dv, int32_t H, int32_t B, int32_t dtype,
+                                  int64_t timeout_us, tylo_stream_t stream);
+int32_t tylo_b200_decode_exchange_status(void* own_buffer, int32_t* code);
+
+/* Device buffers visible to every process of the node (CUDA IPC).  alloc: cudaMalloc + zero fill;
+ * export: writes tylo_b200_peer_handle_bytes() opaque bytes to pass to the other processes by any
+ * host channel; open: maps another process's buffer (peer access is enabled on first use);
+ * close / free undo open / alloc.  Not called on the hot path. */
+int32_t tylo_b200_peer_alloc(void** ptr, int64_t bytes);
+int32_t tylo_b200_peer_free(void* ptr);
+int32_t tylo_b200_peer_handle_bytes(void);
+int32_t tylo_b200_peer_export(const void* ptr, void* handle);
+int32_t tylo_b200_peer_open(void** ptr, const void* handle);
+int32_t tylo_b200_peer_close(void* ptr);
+
 /* ---- softmax -----------------------------------------------------------------------------------
  * softmax! → softmax_fwd / softmax_fwd_single (src/softmax/softmax.jl:96-105, kernels :6-33,:62-72).
  * X, Y (M,N): softmax along dim 1 (the contiguous one), one column per n. */

@@ -69,6 +69,10 @@ _lib.tylo_b200_device_status.restype = c_int32
 _lib.tylo_b200_device_status.argtypes = [POINTER(c_int32)]
 _lib.tylo_b200_decode_suggest_splits.restype = c_int32
 _lib.tylo_b200_decode_suggest_splits.argtypes = [c_int32] * 3
+_lib.tylo_b200_decode_exchange_bytes.restype = c_int64
+_lib.tylo_b200_decode_exchange_bytes.argtypes = [c_int32] * 4
+_lib.tylo_b200_peer_handle_bytes.restype = c_int32
+_lib.tylo_b200_peer_handle_bytes.argtypes = []
 
 _i32, _i64, _f32, _ptr = c_int32, c_int64, c_float, c_void_p
 _SIGS = {
@@ -79,6 +83,13 @@ _SIGS = {
     "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_combine": [_ptr] * 7 + [_i32, _i64, _i64] + [_i32] * 4 + [_ptr],
+    "tylo_b200_decode_exchange": [_ptr] * 4 + [_i32, _i64, _i64, POINTER(c_void_p)] + [_i32] * 6 + [_i64, _ptr],
+    "tylo_b200_decode_exchange_status": [_ptr, POINTER(c_int32)],
+    "tylo_b200_peer_alloc": [POINTER(c_void_p), _i64],
+    "tylo_b200_peer_free": [_ptr],
+    "tylo_b200_peer_export": [_ptr, _ptr],
+    "tylo_b200_peer_open": [POINTER(c_void_p), _ptr],
+    "tylo_b200_peer_close": [_ptr],
     "tylo_b200_softmax_fwd": [_ptr, _ptr, _i64, _i64, _i32, _ptr],
     "tylo_b200_softmax_bwd": [_ptr, _ptr, _ptr, _i64, _i64, _i32, _ptr],
     "tylo_b200_rms_norm_fwd": [_ptr] * 4 + [_i64, _i64, _f32, _f32, _i32, _ptr],
@@ -606,6 +617,101 @@ def decode_combine_(O, O_partial, M_partial, L_partial, *, n_splits, o_stride, m
         mo, mm, ml = merged
     _check(_lib.tylo_b200_decode_combine(_p(O), _p(mo), _p(mm), _p(ml), _p(O_partial), _p(M_partial), _p(L_partial),
                                          int(n_splits), int(o_stride), int(ml_stride), Dv, H, B, dt, _stream()))
+
+
+class DecodeExchange:
+    """Receive buffers for decode with one sequence's KV cache sharded over the GPUs of a node.
+
+    Each rank allocates one buffer through the library (cudaMalloc, zeroed), the CUDA IPC handles
+    travel over ``group`` (any torch.distributed backend), and every rank maps all of them.
+    ``exchange_`` then merges this rank's split partials with every peer's in one launch over
+    NVLink.  With ``group=None`` the object is a single-rank exchange (world 1).  The merge algebra
+    is the reference's (mha_decode_combine, decode.jl:119-140); the reference itself is single-GPU.
+    """
+
+    def __init__(self, B: int, H: int, Dv: int, *, group=None, rank: int = 0, world: int = 1, timeout_us: int = 0):
+        self.B, self.H, self.Dv, self.rank, self.world = B, H, Dv, rank, world
+        self.timeout_us = int(timeout_us)
+        self.nbytes = int(_lib.tylo_b200_decode_exchange_bytes(world, Dv, H, B))
+        if self.nbytes <= 0:
+            raise TyloError(1, f"decode exchange: unsupported extents (world={world}, Dv={Dv}, H={H}, B={B})")
+        own = c_void_p()
+        _check(_lib.tylo_b200_peer_alloc(ctypes.byref(own), self.nbytes))
+        self._own = own
+        self._opened = []
+        ptrs = [None] * world
+        ptrs[rank] = own.value
+        if world > 1:
+            import torch.distributed as dist
+            hb = int(_lib.tylo_b200_peer_handle_bytes())
+            handle = ctypes.create_string_buffer(hb)
+            _check(_lib.tylo_b200_peer_export(own, handle))
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for r in range(world):
+                if r == rank:
+                    continue
+                p = c_void_p()
+                _check(_lib.tylo_b200_peer_open(ctypes.byref(p), ctypes.create_string_buffer(handles[r], hb)))
+                self._opened.append(p)
+                ptrs[r] = p.value
+            dist.barrier(group=group)       # every buffer is zeroed and mapped before the first launch
+        self._peers = (c_void_p * world)(*ptrs)
+
+    @classmethod
+    def local_group(cls, B: int, H: int, Dv: int, *, world: int, timeout_us: int = 0):
+        """``world`` exchange objects inside ONE process on the current GPU, wired to each other's buffers:
+        one process driving several shards in turn.  A rank whose peers have not pushed yet gives up
+        after ``timeout_us``; a rank called after all its peers finds their records and completes."""
+        nbytes = int(_lib.tylo_b200_decode_exchange_bytes(world, Dv, H, B))
+        if nbytes <= 0:
+            raise TyloError(1, f"decode exchange: unsupported extents (world={world}, Dv={Dv}, H={H}, B={B})")
+        bufs = []
+        for _ in range(world):
+            p = c_void_p()
+            _check(_lib.tylo_b200_peer_alloc(ctypes.byref(p), nbytes))
+            bufs.append(p)
+        out = []
+        for r in range(world):
+            x = object.__new__(cls)
+            x.B, x.H, x.Dv, x.rank, x.world, x.timeout_us, x.nbytes = B, H, Dv, r, world, int(timeout_us), nbytes
+            x._own, x._opened = bufs[r], []
+            x._peers = (c_void_p * world)(*[b.value for b in bufs])
+            out.append(x)
+        return out
+
+    def exchange_(self, O, scratch: "DecodeScratch"):
+        """Merges ``scratch`` (this rank's split partials) across all ranks into O (B, H, Dv)."""
+        n_splits = scratch.O_partial.shape[0]
+        B, H, Dv = self.B, self.H, self.Dv
+        assert tuple(O.shape) == (B, H, Dv) and tuple(scratch.O_partial.shape[1:]) == (B, H, Dv)
+        _dense(O, *scratch)
+        _check(_lib.tylo_b200_decode_exchange(_p(O), _p(scratch.O_partial), _p(scratch.M_partial),
+                                              _p(scratch.L_partial), n_splits, B * H * Dv, B * H, self._peers,
+                                              self.rank, self.world, Dv, H, B, _dtype(O), self.timeout_us,
+                                              _stream()))
+        return O
+
+    def status(self) -> int:
+        """Synchronises; 0 if every wait of the calls so far was served, else raises TyloError (status 6)."""
+        code = c_int32(0)
+        _check(_lib.tylo_b200_decode_exchange_status(self._own, ctypes.byref(code)))
+        return int(code.value)
+
+    def close(self):
+        for p in self._opened:
+            _lib.tylo_b200_peer_close(p)
+        self._opened = []
+        if self._own is not None:
+            _lib.tylo_b200_peer_free(self._own)
+            self._own = None
+
+
+def sharded_decode_attention_(O, Q, K_local, V_local, *, lengths_local, exchange: DecodeExchange, scratch):
+    """decode_attention! with the keys of every sequence sharded over ranks: split kernel on the local
+    keys (``lengths_local`` = live keys inside this rank's range), then one exchange launch."""
+    decode_split_(Q, K_local, V_local, lengths=lengths_local, scratch=scratch)
+    return exchange.exchange_(O, scratch)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "decode_merge.cuh"
 
 namespace tylo {
 
@@ -86,6 +87,8 @@ decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const 
   static_assert(WARP_BYTES >= 16 * D * 4 + 128, "merge staging must fit in the warp's ring");
   extern __shared__ __align__(128) uint8_t smem[];
 
+  dependency_wait();         // this kernel may have been placed while the one before it was finishing
+  dependents_may_launch();   // the merge kernel behind this one may be placed while the splits still run
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x % n_splits;
   const int hkb = blockIdx.x / n_splits;
@@ -390,6 +393,28 @@ decode_combine_kernel(T* __restrict__ O, float* __restrict__ Om, float* __restri
   }
 }
 
+// Block-parallel form (Dv % 4 == 0, 16-byte aligned partials): 1024 threads fold the partials with
+// independent vector loads, see merge_partials.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+decode_combine_wide_kernel(T* __restrict__ O, float* __restrict__ Om, float* __restrict__ Mm, float* __restrict__ Lm,
+                           const float* __restrict__ Op, const float* __restrict__ Mp, const float* __restrict__ Lp,
+                           int n_splits, int64_t o_stride, int64_t ml_stride, int Dv) {
+  extern __shared__ __align__(16) float wsm[];
+  float* res = wsm + 4096 + 64;
+  const int hb = blockIdx.x;
+  const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+  dependency_wait();
+  dependents_may_launch();
+  float m, l;
+  merge_partials<false>(Op + (size_t)hb * Dv, Mp + hb, Lp + hb, n_splits, o_stride, ml_stride, Dv, wsm, res, m, l);
+  if (tid < Dv) {
+    if (O) O[(size_t)hb * Dv + tid] = Elem<T>::from_f(res[tid]);
+    if (Om) Om[(size_t)hb * Dv + tid] = res[tid];
+  }
+  if (tid == 0 && Mm) { Mm[hb] = m; Lm[hb] = l; }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 static int decode_split_size(int Sk, int n_splits) {
   const int per = (Sk + n_splits - 1) / n_splits;
@@ -408,13 +433,15 @@ static int32_t launch_decode_mma(const void* Q, const void* K, const void* V, co
   if (G <= 8) {
     auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, false>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    kern<<<grid, NWARPS * 32, SMEM, st>>>((const T*)Q, (const T*)K, (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv,
-                                          B, G, n_splits, split_size, scale_log2);
+    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 2) != 0, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
+                                   (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
+                                   scale_log2));
   } else {
     auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, true>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    kern<<<grid, NWARPS * 32, SMEM, st>>>((const T*)Q, (const T*)K, (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv,
-                                          B, G, n_splits, split_size, scale_log2);
+    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 2) != 0, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
+                                   (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
+                                   scale_log2));
   }
   return check_launch("decode_split_mma");
 }
@@ -466,6 +493,12 @@ static int32_t decode_combine_dispatch(void* O, float* Om, float* Mm, float* Lm,
                                        int H, int B, cudaStream_t st) {
   const int tx = Dv >= 128 ? 128 : (Dv >= 64 ? 64 : 32);
   const unsigned grid = (unsigned)((int64_t)H * B);
+  if (n_splits > 2 && Dv % 4 == 0 && Dv <= 512 && aligned16(Op) && o_stride % 4 == 0) {
+    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 1) != 0, decode_combine_wide_kernel<T>, dim3(grid), merge_block(Dv),
+                                   merge_smem_floats(1024, Dv) * sizeof(float), st, (T*)O, Om, Mm, Lm, Op, Mp, Lp,
+                                   n_splits, o_stride, ml_stride, Dv));
+    return check_launch("decode_combine_wide");
+  }
   if (n_splits > 8) {
     constexpr int SL = 8;
     decode_combine_kernel<T, SL><<<grid, dim3(tx, SL), (SL * Dv + SL) * sizeof(float), st>>>(
