@@ -493,7 +493,9 @@ static int32_t decode_combine_dispatch(void* O, float* Om, float* Mm, float* Lm,
                                        int H, int B, cudaStream_t st) {
   const int tx = Dv >= 128 ? 128 : (Dv >= 64 ? 64 : 32);
   const unsigned grid = (unsigned)((int64_t)H * B);
-  if (n_splits > 2 && Dv % 4 == 0 && Dv <= 512 && aligned16(Op) && o_stride % 4 == 0) {
+  // Many partials per head (long contexts): the 1024-thread block-parallel merge.  Few partials: a small
+  // block per head, or a thousand mostly idle threads per head would cost more than the merge itself.
+  if (n_splits > 16 && Dv % 4 == 0 && Dv <= 512 && aligned16(Op) && o_stride % 4 == 0) {
     TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 1) != 0, decode_combine_wide_kernel<T>, dim3(grid), merge_block(Dv),
                                    merge_smem_floats(1024, Dv) * sizeof(float), st, (T*)O, Om, Mm, Lm, Op, Mp, Lp,
                                    n_splits, o_stride, ml_stride, Dv));

@@ -1,4 +1,4 @@
-export decode_attention!
+export decode_attention!, sharded_decode_attention!, DecodeExchange, exchange_status
 
 "A split count that fills the GPU for this cache (the reference's fixed 8 gives 8·Hkv·B blocks)."
 suggest_splits(Sk, Hkv, B) =
@@ -46,4 +46,89 @@ function allocate_scratchspace(::typeof(decode_attention!), O, Q; n_splits = 8)
     return (; O_partial = similar(O, Float32, (Dv, H, B, n_splits)),
               M_partial = similar(O, Float32, (H, B, n_splits)),
               L_partial = similar(O, Float32, (H, B, n_splits)))
+end
+
+# ---- one sequence's keys sharded over the GPUs of a node (no counterpart in the reference) ------------
+
+"""
+    DecodeExchange(O; rank, world, share, timeout_us = 0)
+
+Receive buffer of this process for sharded decode, mapped into every process of the node.
+`share(handle::Vector{UInt8}) -> Vector{Vector{UInt8}}` is the host channel: it must return the
+handles of all ranks in rank order (an MPI allgather, a file, a socket — 64 bytes per rank) and act
+as a barrier.  The buffer lives until `close(ex)`.
+"""
+mutable struct DecodeExchange
+    own::Ptr{Cvoid}
+    peers::Vector{Ptr{Cvoid}}
+    opened::Vector{Ptr{Cvoid}}
+    rank::Int32
+    world::Int32
+    timeout_us::Int64
+end
+
+function DecodeExchange(O; rank::Integer, world::Integer, share, timeout_us::Integer = 0)
+    Dv, H, B = size(O)
+    nbytes = ccall((:tylo_b200_decode_exchange_bytes, libtylo), Int64, (Int32, Int32, Int32, Int32), world, Dv, H, B)
+    nbytes > 0 || throw(ArgumentError("decode exchange: unsupported extents (world=$world, Dv=$Dv)"))
+    own = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:tylo_b200_peer_alloc, libtylo), Int32, (Ptr{Ptr{Cvoid}}, Int64), own, nbytes))
+    hb = ccall((:tylo_b200_peer_handle_bytes, libtylo), Int32, ())
+    handle = zeros(UInt8, hb)
+    check(ccall((:tylo_b200_peer_export, libtylo), Int32, (Ptr{Cvoid}, Ptr{UInt8}), own[], handle))
+    handles = world > 1 ? share(handle) : [handle]
+    peers = Vector{Ptr{Cvoid}}(undef, world); opened = Ptr{Cvoid}[]
+    for r in 0:world-1
+        if r == rank
+            peers[r + 1] = own[]
+        else
+            p = Ref{Ptr{Cvoid}}(C_NULL)
+            check(ccall((:tylo_b200_peer_open, libtylo), Int32, (Ptr{Ptr{Cvoid}}, Ptr{UInt8}), p, handles[r + 1]))
+            peers[r + 1] = p[]; push!(opened, p[])
+        end
+    end
+    return DecodeExchange(own[], peers, opened, Int32(rank), Int32(world), Int64(timeout_us))
+end
+
+function Base.close(ex::DecodeExchange)
+    foreach(p -> ccall((:tylo_b200_peer_close, libtylo), Int32, (Ptr{Cvoid},), p), ex.opened)
+    empty!(ex.opened)
+    ex.own == C_NULL || ccall((:tylo_b200_peer_free, libtylo), Int32, (Ptr{Cvoid},), ex.own)
+    ex.own = C_NULL
+    return nothing
+end
+
+"""
+    sharded_decode_attention!(O, Q, K_local, V_local; lengths_local, exchange, scratch) -> O
+
+`decode_attention!` when this process holds only a key range of every sequence: the split kernel on
+the local keys, then one launch that merges the local splits, exchanges the merged records with all
+peers over NVLink and writes the final `O` on every rank.  All ranks call it in the same order.
+"""
+function sharded_decode_attention!(O, Q, K, V; lengths_local, exchange::DecodeExchange, scratch)
+    Dk, Sk, Hkv, B = size(K)
+    Dv, H, _ = size(O)
+    (; O_partial, M_partial, L_partial) = scratch
+    ns = size(O_partial, 4)
+    require_dense(O, Q, K, V, lengths_local, O_partial, M_partial, L_partial)
+    check(ccall((:tylo_b200_decode_split, libtylo), Int32,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+         Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Ptr{Cvoid}),
+        devptr(Q), devptr(K), devptr(V), devptr(lengths_local), devptr(O_partial), devptr(M_partial),
+        devptr(L_partial), Int32(ns), Int32(Dk), Int32(Dv), Int32(Sk), Int32(H), Int32(Hkv), Int32(B),
+        tylo_dtype(eltype(Q)), current_stream()))
+    check(ccall((:tylo_b200_decode_exchange, libtylo), Int32,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int64, Int64, Ptr{Ptr{Cvoid}},
+         Int32, Int32, Int32, Int32, Int32, Int32, Int64, Ptr{Cvoid}),
+        devptr(O), devptr(O_partial), devptr(M_partial), devptr(L_partial), Int32(ns), Int64(H * B * Dv),
+        Int64(H * B), exchange.peers, exchange.rank, exchange.world, Int32(Dv), Int32(H), Int32(B),
+        tylo_dtype(eltype(O)), exchange.timeout_us, current_stream()))
+    return O
+end
+
+"Synchronises; throws if a peer's record did not arrive within the time limit in an earlier call."
+function exchange_status(ex::DecodeExchange)
+    code = Ref{Int32}(0)
+    check(ccall((:tylo_b200_decode_exchange_status, libtylo), Int32, (Ptr{Cvoid}, Ptr{Int32}), ex.own, code))
+    return Int(code[])
 end
