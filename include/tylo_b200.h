@@ -82,7 +82,11 @@ typedef struct {
 
 #define TYLO_SCORE_ALIBI 1u         /* AliBiScore: s + slopes[h] * (q - kv), one slope per query head (mods.jl:205-209) */
 #define TYLO_SCORE_SOFTCAP 2u       /* SoftCapScore: cap * tanh(s / cap) (mods.jl:194-198) */
-#define TYLO_SCORE_SOFTCAP_FIRST 4u /* with both set: 0 = softcap ∘ alibi (alibi first), 1 = alibi ∘ softcap (mods.jl:244-249) */
+#define TYLO_SCORE_SOFTCAP_FIRST 4u /* with soft cap and an additive mod: 0 = softcap ∘ additive (additive first),
+                                       1 = additive ∘ softcap (mods.jl:244-249) */
+#define TYLO_SCORE_BIAS 8u          /* BiasScore: s + bias[kv, q, mod1(h,nh), mod1(b,nb)] with LOCAL row indices
+                                       q, kv (not shifted by input_pos) (mods.jl:212-237).  ALiBi and bias are both
+                                       additive and sit at the same place of the chain. */
 
 typedef struct {
   uint32_t flags;
@@ -90,6 +94,12 @@ typedef struct {
   const float* slopes; /* device fp32, length H */
   float* d_slopes;     /* backward only, nullable: accumulates the slope gradient atomically
                           (grad_shadow semantics, mods.jl:296-303); caller zeroes it */
+  const float* bias;   /* device fp32 (Sk, Sq, bias_heads, bias_batch), dense column-major; heads and batch
+                          broadcast by mod1 when bias_heads < H or bias_batch < B */
+  float* d_bias;       /* backward only, nullable: same shape, accumulated atomically (mods.jl:305-313);
+                          caller zeroes it */
+  int32_t bias_heads;
+  int32_t bias_batch;
 } tylo_score_desc;
 
 /* ---- fused attention ---------------------------------------------------------------------------

@@ -86,28 +86,38 @@ class ScoreSpec:
     def __init__(self, ops=()):
         self.ops = list(ops)
 
-    def apply(self, s0, h, q_pos, kv_pos):
+    @staticmethod
+    def _bias_slice(par, b, h):
+        """bias[kv+1, q+1, mod1(h, nh), mod1(b, nb)] on LOCAL rows (mods.jl:236-237); the table is
+        held as (nb, nh, Sq, Sk)."""
+        t = np.asarray(par, dtype=F64)
+        return t[b % t.shape[0], h % t.shape[1]]
+
+    def _step(self, kind, par, s, b, h, rel):
+        if kind == "softcap":
+            return float(par) * np.tanh(s / float(par))
+        if kind == "alibi":
+            return s + float(np.asarray(par, dtype=F64)[h]) * rel
+        if kind == "bias":
+            return s + self._bias_slice(par, b, h)
+        raise ValueError(kind)
+
+    def apply(self, s0, h, q_pos, kv_pos, b=0):
         s = s0
         rel = (q_pos[:, None] - kv_pos[None, :]).astype(F64)
         for kind, par in self.ops:
-            if kind == "softcap":
-                s = float(par) * np.tanh(s / float(par))
-            elif kind == "alibi":
-                s = s + float(np.asarray(par, dtype=F64)[h]) * rel
-            else:
-                raise ValueError(kind)
+            s = self._step(kind, par, s, b, h, rel)
         return s
 
-    def vjp(self, s0, h, q_pos, kv_pos, sbar):
-        """VJP at the PRE-mod score (mods.jl:288-319): returns (s0bar, {op index: slope grad})."""
+    def vjp(self, s0, h, q_pos, kv_pos, sbar, b=0):
+        """VJP at the PRE-mod score (mods.jl:288-319): returns (s0bar, {op index: parameter grad}):
+        a scalar slope gradient for an ALiBi op (mods.jl:296-303), the (Sq, Sk) gradient of this
+        (b, h) slice for a bias op (mods.jl:305-313)."""
         rel = (q_pos[:, None] - kv_pos[None, :]).astype(F64)
         inter = [s0]
         s = s0
         for kind, par in self.ops:
-            if kind == "softcap":
-                s = float(par) * np.tanh(s / float(par))
-            else:
-                s = s + float(np.asarray(par, dtype=F64)[h]) * rel
+            s = self._step(kind, par, s, b, h, rel)
             inter.append(s)
         g = sbar
         pgrads = {}
@@ -116,8 +126,10 @@ class ScoreSpec:
             if kind == "softcap":
                 th = np.tanh(inter[i] / float(par))
                 g = g * (1.0 - th * th)
-            else:
+            elif kind == "alibi":
                 pgrads[i] = float(np.sum(g * rel))
+            else:
+                pgrads[i] = g.copy()
         return g, pgrads
 
 
@@ -168,7 +180,7 @@ def flex_ref(Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec | None =
             hk = h // g                          # cld(h, g) on 1-based h (attention.jl:23)
             S = (Q[b, h] @ K[b, hk].T) * scale   # (Sq, Sk)
             if score is not None:
-                S = score.apply(S, h, q_pos, kv_pos)
+                S = score.apply(S, h, q_pos, kv_pos, b)
             if keep is not None:
                 S = np.where(keep, S, -np.inf)
             P, mx, den = _softmax_cols(S)
@@ -202,6 +214,8 @@ def flex_bwd_ref(dO, Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec 
         for i, (kind, par) in enumerate(score.ops):
             if kind == "alibi":
                 slope_grads[i] = np.zeros(H, F64)
+            elif kind == "bias":
+                slope_grads[i] = np.zeros(np.asarray(par).shape, F64)
     keep_shared = None
     if mask is not None and doc_per_batch is None:
         keep_shared = mask.dense(q_pos, kv_pos)
@@ -214,7 +228,7 @@ def flex_bwd_ref(dO, Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec 
         for h in range(H):
             hk = h // g
             S0 = (Q[b, h] @ K[b, hk].T) * scale
-            S = S0 if score is None else score.apply(S0, h, q_pos, kv_pos)
+            S = S0 if score is None else score.apply(S0, h, q_pos, kv_pos, b)
             if keep is not None:
                 S = np.where(keep, S, -np.inf)
             P, _, _ = _softmax_cols(S)
@@ -222,9 +236,13 @@ def flex_bwd_ref(dO, Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec 
             dP = do @ V[b, hk].T                            # (Sq, Sk)
             dS = P * (dP - np.sum(P * dP, axis=-1, keepdims=True))
             if score is not None:
-                dS0, pg = score.vjp(S0, h, q_pos, kv_pos, dS)
+                dS0, pg = score.vjp(S0, h, q_pos, kv_pos, dS, b)
                 for i, val in pg.items():
-                    slope_grads[i][h] += val
+                    if score.ops[i][0] == "alibi":
+                        slope_grads[i][h] += val
+                    else:                       # heads / batch entries that share a table slice add up
+                        t = slope_grads[i]
+                        t[b % t.shape[0], h % t.shape[1]] += val
             else:
                 dS0 = dS
             dQ[b, h] = (dS0 @ K[b, hk]) * scale

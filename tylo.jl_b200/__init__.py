@@ -40,7 +40,7 @@ F32, BF16, F16 = 0, 1, 2
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 MASK_CAUSAL, MASK_SLIDING, MASK_DOCUMENT, MASK_PREFIX, MASK_PREFIX_LM = 1, 2, 4, 8, 16
-SCORE_ALIBI, SCORE_SOFTCAP, SCORE_SOFTCAP_FIRST = 1, 2, 4
+SCORE_ALIBI, SCORE_SOFTCAP, SCORE_SOFTCAP_FIRST, SCORE_BIAS = 1, 2, 4, 8
 
 
 class _MaskDesc(Structure):
@@ -50,7 +50,8 @@ class _MaskDesc(Structure):
 
 
 class _ScoreDesc(Structure):
-    _fields_ = [("flags", c_uint32), ("cap", c_float), ("slopes", c_void_p), ("d_slopes", c_void_p)]
+    _fields_ = [("flags", c_uint32), ("cap", c_float), ("slopes", c_void_p), ("d_slopes", c_void_p),
+                ("bias", c_void_p), ("d_bias", c_void_p), ("bias_heads", c_int32), ("bias_batch", c_int32)]
 
 
 class TyloError(RuntimeError):
@@ -272,6 +273,21 @@ class AliBiScore(ScoreMod):
         return s + float(self.slopes[h - 1]) * (q - kv)
 
 
+class BiasScore(ScoreMod):
+    """``s + bias[kv, q, mod1(h, nh), mod1(b, nb)]`` (mods.jl:212-237).  ``bias`` is a float32 tensor
+    (nb, nh, Sq, Sk) — Julia's (Sk, Sq, nh, nb) — indexed by local rows: q and kv are not shifted by
+    ``input_pos``.  Runs on the fp32-arithmetic kernels."""
+
+    def __init__(self, bias: torch.Tensor):
+        if bias.dim() != 4:
+            raise ValueError("BiasScore expects (bias_batch, bias_heads, Sq, Sk)")
+        self.bias = bias
+
+    def __call__(self, s, b, h, q, kv):
+        nb, nh = self.bias.shape[:2]
+        return s + float(self.bias[(b - 1) % nb, (h - 1) % nh, q, kv])
+
+
 class ComposeScore(ScoreMod):
     """Apply ``a`` then ``b`` (mods.jl:244-249)."""
 
@@ -298,6 +314,8 @@ def grad_shadow(x):
         return torch.zeros_like(x)
     if isinstance(x, AliBiScore):
         return AliBiScore(torch.zeros_like(x.slopes))
+    if isinstance(x, BiasScore):
+        return BiasScore(torch.zeros_like(x.bias))
     if isinstance(x, ComposeScore):
         return ComposeScore(grad_shadow(x.a), grad_shadow(x.b))
     return x
@@ -374,13 +392,30 @@ def _score_desc(m: Optional[ScoreMod], dm, keep: list) -> _ScoreDesc:
         chain.append((x, dx))
 
     walk(m, dm)
+    # The additive mods (ALiBi, bias) share one place in the chain: all before or all after the soft cap.
+    caps = [i for i, (x, _) in enumerate(chain) if isinstance(x, SoftCapScore)]
+    adds = [i for i, (x, _) in enumerate(chain) if isinstance(x, (AliBiScore, BiasScore))]
+    if caps and adds and not (max(adds) < caps[0] or min(adds) > caps[0]):
+        _unsupported("additive score mods on both sides of a SoftCapScore")
     for i, (x, dx) in enumerate(chain):
         if isinstance(x, SoftCapScore):
             if d.flags & SCORE_SOFTCAP:
                 _unsupported("more than one SoftCapScore")
             d.flags |= SCORE_SOFTCAP; d.cap = x.cap
-            if not d.flags & SCORE_ALIBI and any(isinstance(y, AliBiScore) for y, _ in chain[i + 1:]):
+            if adds and min(adds) > i:
                 d.flags |= SCORE_SOFTCAP_FIRST
+        elif isinstance(x, BiasScore):
+            if d.flags & SCORE_BIAS:
+                _unsupported("more than one BiasScore")
+            if x.bias.dtype != torch.float32:
+                raise TypeError("BiasScore bias must be float32")
+            _dense(x.bias)
+            d.flags |= SCORE_BIAS; d.bias = x.bias.data_ptr(); keep.append(x.bias)
+            d.bias_batch, d.bias_heads = int(x.bias.shape[0]), int(x.bias.shape[1])
+            d._bias_shape = tuple(x.bias.shape[2:])
+            if dx is not None:
+                _dense(dx.bias)
+                d.d_bias = dx.bias.data_ptr(); keep.append(dx.bias)
         elif isinstance(x, AliBiScore):
             if d.flags & SCORE_ALIBI:
                 _unsupported("more than one AliBiScore")
@@ -493,6 +528,12 @@ allocate_checkpoints_flex_attention = allocate_checkpoints_attention       # fle
 allocate_scratchspace_grad_flex_attention = allocate_scratchspace_grad_attention  # flex.jl:519-522
 
 
+def _check_bias_shape(sd: _ScoreDesc, Sq: int, Sk: int) -> None:
+    shape = getattr(sd, "_bias_shape", None)
+    if shape is not None and shape != (Sq, Sk):
+        raise ValueError(f"BiasScore bias covers {shape} (Sq, Sk) pairs but the call has ({Sq}, {Sk})")
+
+
 def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=None, block_sparse=True,
                     input_pos=0, qk_scale=None, checkpoints=None):
     """flex_attention!(O, Q, K, V; score_mod, mask_mod, ...) (flex.jl:312-383)."""
@@ -504,6 +545,7 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
     keep: list = []
     md = _mask_desc(mask_mod, keep)
     sd = _score_desc(score_mod, None, keep)
+    _check_bias_shape(sd, Sq, Sk)
     M = None if checkpoints is None else checkpoints.M
     L = None if checkpoints is None else checkpoints.L
     _check(_lib.tylo_b200_flex_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md),
@@ -532,6 +574,7 @@ def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplica
     keep: list = []
     md = _mask_desc(mask_mod, keep)
     sd = _score_desc(score_mod, d_score_mod, keep)
+    _check_bias_shape(sd, Sq, Sk)
     ws = scratch.workspace
     _check(_lib.tylo_b200_flex_attention_bwd(_p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV),
                                              _p(pO), _p(dO), _p(checkpoints.M), _p(checkpoints.L),

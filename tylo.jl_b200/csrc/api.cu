@@ -29,6 +29,7 @@ static int32_t check_attn_dims(const char* who, int Dk, int Dv, int Sq, int Sk, 
 static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* mask, const tylo_score_desc* score) {
   p.mask_flags = 0; p.window = 0; p.prefix_len = 0; p.doc_q = nullptr; p.doc_kv = nullptr; p.doc_stride = 0;
   p.score_flags = 0; p.cap = 1.f; p.slopes = nullptr; p.d_slopes = nullptr;
+  p.bias = nullptr; p.d_bias = nullptr; p.bias_heads = 1; p.bias_batch = 1;
   if (mask) {
     const uint32_t known = TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING | TYLO_MASK_DOCUMENT | TYLO_MASK_PREFIX |
                            TYLO_MASK_PREFIX_LM;
@@ -49,7 +50,7 @@ static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* m
     }
   }
   if (score) {
-    const uint32_t known = TYLO_SCORE_ALIBI | TYLO_SCORE_SOFTCAP | TYLO_SCORE_SOFTCAP_FIRST;
+    const uint32_t known = TYLO_SCORE_ALIBI | TYLO_SCORE_SOFTCAP | TYLO_SCORE_SOFTCAP_FIRST | TYLO_SCORE_BIAS;
     TYLO_REQUIRE((score->flags & ~known) == 0, TYLO_ERR_UNSUPPORTED, "%s: unknown score flags 0x%x", who,
                  score->flags);
     p.score_flags = score->flags;
@@ -61,6 +62,13 @@ static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* m
     if (score->flags & TYLO_SCORE_ALIBI) {
       TYLO_REQUIRE(score->slopes, TYLO_ERR_INVALID_ARGUMENT, "%s: AliBiScore needs slopes", who);
       p.slopes = score->slopes; p.d_slopes = score->d_slopes;
+    }
+    if (score->flags & TYLO_SCORE_BIAS) {
+      TYLO_REQUIRE(score->bias, TYLO_ERR_INVALID_ARGUMENT, "%s: BiasScore needs a bias table", who);
+      TYLO_REQUIRE(score->bias_heads > 0 && score->bias_batch > 0, TYLO_ERR_INVALID_ARGUMENT,
+                   "%s: BiasScore extents must be positive (heads %d, batch %d)", who, score->bias_heads,
+                   score->bias_batch);
+      p.bias = score->bias; p.d_bias = score->d_bias; p.bias_heads = score->bias_heads; p.bias_batch = score->bias_batch;
     }
   }
   return TYLO_OK;

@@ -125,7 +125,7 @@ attn_fwd_generic_kernel(T* __restrict__ O, const T* __restrict__ Q, const T* __r
       for (int j = 0; j < 2; ++j) {
         const int kv = kv0 + c0 + j;
         const bool ok = row < p.Sq && kv < k_len && mask_keep(p, b, qpos, kv);
-        s[i][j] = ok ? score_apply(p, s[i][j] * p.scale, slope, qpos, kv) * kLog2e : -INFINITY;
+        s[i][j] = ok ? score_apply(p, s[i][j] * p.scale, score_additive(p, slope, b, h, row, qpos, kv)) * kLog2e : -INFINITY;
         mx = fmaxf(mx, s[i][j]);
       }
       mx = half_warp_max(mx);
@@ -199,7 +199,8 @@ attn_bwd_delta_kernel(float* __restrict__ Delta, const T* __restrict__ O, const 
 // pre-mod score gradient.  Returns the ALiBi slope-gradient contribution of the patch.
 struct BwdPatch { float p[2][2], ds0[2][2]; };
 
-__device__ __forceinline__ float bwd_patch(const AttnParams& p, int b, float slope, const float* sQ,
+template <bool PARAM_GRADS>
+__device__ __forceinline__ float bwd_patch(const AttnParams& p, int b, int h, float slope, const float* sQ,
                                            const float* sK, const float* sdO, const float* sV, int ldk,
                                            int ldv, int Dk4, int Dv4, int q0, int kv0, int r0, int c0,
                                            int q_lim, int k_len, const float* sLse, const float* sDelta,
@@ -218,13 +219,16 @@ __device__ __forceinline__ float bwd_patch(const AttnParams& p, int b, float slo
       float pv = 0.f, g0 = 0.f;
       if (ok) {
         const float s0 = s[i][j] * p.scale;
-        const float t = score_apply(p, s0, slope, qpos, kv) * kLog2e;
+        const float add = score_additive(p, slope, b, h, row, qpos, kv);
+        const float t = score_apply(p, s0, add) * kLog2e;
         const float lse = sLse[r0 + i];
         pv = (lse == -INFINITY) ? 0.f : exp2f(t - lse);
         const float ds = pv * (dp[i][j] - sDelta[r0 + i]);
-        float at_alibi;
-        g0 = score_vjp(p, s0, slope, qpos, kv, ds, &at_alibi);
-        slope_acc += at_alibi * (float)(qpos - kv);
+        float at_add;
+        g0 = score_vjp(p, s0, add, ds, &at_add);
+        slope_acc += at_add * (float)(qpos - kv);
+        // broadcast heads / batch entries share a table entry: accumulate atomically (mods.jl:305-313)
+        if (PARAM_GRADS && p.d_bias && (p.score_flags & TYLO_SCORE_BIAS)) atomicAdd(p.d_bias + bias_index(p, b, h, row, kv), at_add);
       }
       out.p[i][j] = pv;
       out.ds0[i][j] = g0 * p.scale;
@@ -289,7 +293,7 @@ attn_bwd_dkdv_generic_kernel(T* __restrict__ dK, T* __restrict__ dV, const T* __
       }
       __syncthreads();
       BwdPatch bp;
-      bwd_patch(p, b, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len, sLse, sDelta, bp);
+      bwd_patch<false>(p, b, h, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len, sLse, sDelta, bp);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -394,7 +398,7 @@ attn_bwd_dq_generic_kernel(T* __restrict__ dQ, const T* __restrict__ Q, const T*
     load_tile(sV, ldv, Vg, kv0, p.Sk, p.Dv, Dv4);
     __syncthreads();
     BwdPatch bp;
-    slope_acc += bwd_patch(p, b, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len,
+    slope_acc += bwd_patch<true>(p, b, h, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len,
                            sLse, sDelta, bp);
 #pragma unroll
     for (int i = 0; i < 2; ++i)

@@ -21,6 +21,9 @@ struct AttnParams {
   float cap;
   const float* slopes;
   float* d_slopes;
+  const float* bias;      // (Sk, Sq, bias_heads, bias_batch) fp32, local row indices
+  float* d_bias;
+  int bias_heads, bias_batch;
   const int32_t* k_lengths;
   const int32_t* q_lengths;
   int natural_stats;      // 1: M/L in natural units (flex), 0: log2 units (attention!)
@@ -39,30 +42,43 @@ __device__ __forceinline__ bool mask_keep(const AttnParams& p, int b, int q, int
   return keep;
 }
 
-// Score mod chain on the scaled score s0 (mods.jl:188-249).  Returns the modded score.
-__device__ __forceinline__ float score_apply(const AttnParams& p, float s0, float slope, int q, int kv) {
+// Additive part of the score-mod chain for one pair: ALiBi's slope * (q - kv) on absolute positions plus
+// BiasScore's table entry on LOCAL row indices, heads and batch broadcast by modulo (mods.jl:205-237).
+__device__ __forceinline__ size_t bias_index(const AttnParams& p, int b, int h, int row, int kv) {
+  return (((size_t)(b % p.bias_batch) * p.bias_heads + (h % p.bias_heads)) * p.Sq + row) * p.Sk + kv;
+}
+__device__ __forceinline__ float score_additive(const AttnParams& p, float slope, int b, int h, int row, int qpos,
+                                                int kv) {
+  float add = 0.f;
+  if (p.score_flags & TYLO_SCORE_ALIBI) add = slope * (float)(qpos - kv);
+  if (p.score_flags & TYLO_SCORE_BIAS) add += p.bias[bias_index(p, b, h, row, kv)];
+  return add;
+}
+
+// Score mod chain on the scaled score s0 (mods.jl:188-249); `add` = score_additive.  Returns the modded score.
+__device__ __forceinline__ float score_apply(const AttnParams& p, float s0, float add) {
   float s = s0;
-  const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
+  const bool additive = p.score_flags & (TYLO_SCORE_ALIBI | TYLO_SCORE_BIAS), cap = p.score_flags & TYLO_SCORE_SOFTCAP;
   const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
   if (cap && cap_first) s = p.cap * tanhf(s / p.cap);
-  if (alibi) s += slope * (float)(q - kv);
+  if (additive) s += add;
   if (cap && !cap_first) s = p.cap * tanhf(s / p.cap);
   return s;
 }
 
-// VJP of the chain at the pre-mod score (mods.jl:288-319): given ds at the output, returns ds0
-// and the value whose sum times (q - kv) is the ALiBi slope gradient.
-__device__ __forceinline__ float score_vjp(const AttnParams& p, float s0, float slope, int q, int kv, float ds,
-                                           float* ds_at_alibi) {
-  const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
+// VJP of the chain at the pre-mod score (mods.jl:288-319): given ds at the output, returns ds0 and,
+// through ds_at_add, the gradient at the additive mods (times (q - kv) it sums to the ALiBi slope
+// gradient; as it stands it is the bias gradient of the pair).
+__device__ __forceinline__ float score_vjp(const AttnParams& p, float s0, float add, float ds, float* ds_at_add) {
+  const bool additive = p.score_flags & (TYLO_SCORE_ALIBI | TYLO_SCORE_BIAS), cap = p.score_flags & TYLO_SCORE_SOFTCAP;
   const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
   float g = ds;
-  if (cap && !cap_first) {  // softcap is the outer mod: its input is s0 (+ alibi)
-    const float in = alibi ? s0 + slope * (float)(q - kv) : s0;
+  if (cap && !cap_first) {  // softcap is the outer mod: its input is s0 (+ additive mods)
+    const float in = additive ? s0 + add : s0;
     const float th = tanhf(in / p.cap);
     g *= (1.f - th * th);
   }
-  *ds_at_alibi = g;         // additive mod passes the gradient through
+  *ds_at_add = g;           // additive mods pass the gradient through
   if (cap && cap_first) {
     const float th = tanhf(s0 / p.cap);
     g *= (1.f - th * th);

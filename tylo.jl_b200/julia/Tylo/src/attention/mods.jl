@@ -84,7 +84,7 @@ struct AliBiScore{A} <: ScoreMod
 end
 (m::AliBiScore)(s, b, h, q, kv) = s + m.slopes[h] * Float32(q - kv)
 
-"Additive bias `(N_kv, M_q, heads, batch)`.  Host evaluation only: libtylo_b200 has no kernel for it."
+"Additive bias `(N_kv, M_q, heads, batch)`, `Float32`, indexed by local rows (not shifted by `input_pos`); heads and batch broadcast by `mod1`.  Runs on the library's fp32-arithmetic kernels."
 struct BiasScore{A} <: ScoreMod
     bias::A
     nheads::Int32
@@ -109,6 +109,7 @@ fields.  Pass a score-mod shadow as `∂score_mod` to `∇flex_attention!`; vali
 """
 grad_shadow(x::AbstractArray) = fill!(similar(x), 0)
 grad_shadow(m::AliBiScore) = AliBiScore(grad_shadow(m.slopes))
+grad_shadow(m::BiasScore) = BiasScore(grad_shadow(m.bias), m.nheads, m.nbatch)
 grad_shadow(m::ComposeScore) = ComposeScore(grad_shadow(m.a), grad_shadow(m.b))
 grad_shadow(x) = x
 
@@ -116,6 +117,7 @@ grad_shadow(x) = x
 const MASK_CAUSAL = UInt32(1); const MASK_SLIDING = UInt32(2); const MASK_DOCUMENT = UInt32(4)
 const MASK_PREFIX = UInt32(8); const MASK_PREFIX_LM = UInt32(16)
 const SCORE_ALIBI = UInt32(1); const SCORE_SOFTCAP = UInt32(2); const SCORE_SOFTCAP_FIRST = UInt32(4)
+const SCORE_BIAS = UInt32(8)
 
 mutable struct MaskDesc
     flags::UInt32
@@ -135,8 +137,12 @@ mutable struct ScoreDesc
     cap::Float32
     slopes::Ptr{Cvoid}
     d_slopes::Ptr{Cvoid}
+    bias::Ptr{Cvoid}
+    d_bias::Ptr{Cvoid}
+    bias_heads::Int32
+    bias_batch::Int32
 end
-ScoreDesc() = ScoreDesc(0, 1.0f0, C_NULL, C_NULL)
+ScoreDesc() = ScoreDesc(0, 1.0f0, C_NULL, C_NULL, C_NULL, C_NULL, 1, 1)
 
 unsupported(what) = throw(ArgumentError("$what is unsupported by libtylo_b200 (there is no fallback)"))
 
@@ -184,18 +190,27 @@ flatten(m::ScoreMod, ∂m) = Tuple{ScoreMod,Any}[(m, ∂m)]
 function describe(score_mod::ScoreMod, ∂score_mod = nothing)
     d = ScoreDesc()
     chain = flatten(score_mod, ∂score_mod)
+    # the additive mods (ALiBi, bias) share one place in the chain: all before or all after the soft cap
+    caps = findall(x -> x[1] isa SoftCapScore, chain)
+    adds = findall(x -> x[1] isa AliBiScore || x[1] isa BiasScore, chain)
+    if !isempty(caps) && !isempty(adds) && !(maximum(adds) < caps[1] || minimum(adds) > caps[1])
+        unsupported("additive score mods on both sides of a SoftCapScore")
+    end
     for (i, (m, ∂m)) in enumerate(chain)
         if m isa SoftCapScore
             (d.flags & SCORE_SOFTCAP) != 0 && unsupported("more than one SoftCapScore")
             d.flags |= SCORE_SOFTCAP; d.cap = m.cap
-            if (d.flags & SCORE_ALIBI) == 0 && any(x -> x[1] isa AliBiScore, chain[i+1:end])
-                d.flags |= SCORE_SOFTCAP_FIRST
-            end
+            !isempty(adds) && minimum(adds) > i && (d.flags |= SCORE_SOFTCAP_FIRST)
         elseif m isa AliBiScore
             (d.flags & SCORE_ALIBI) != 0 && unsupported("more than one AliBiScore")
             eltype(m.slopes) === Float32 || throw(ArgumentError("AliBiScore slopes must be Float32"))
             d.flags |= SCORE_ALIBI; d.slopes = devptr(m.slopes)
             ∂m === nothing || (d.d_slopes = devptr(∂m.slopes))
+        elseif m isa BiasScore
+            (d.flags & SCORE_BIAS) != 0 && unsupported("more than one BiasScore")
+            eltype(m.bias) === Float32 || throw(ArgumentError("BiasScore bias must be Float32"))
+            d.flags |= SCORE_BIAS; d.bias = devptr(m.bias); d.bias_heads = m.nheads; d.bias_batch = m.nbatch
+            ∂m === nothing || (d.d_bias = devptr(∂m.bias))
         else
             unsupported("score mod $(typeof(m))")
         end
