@@ -141,8 +141,8 @@ def make_prefill(t, torch, seed, bwd=False):
     if not bwd:
         w.update(step=lambda: t.attention_(O, Q, K, V, causal=True, checkpoints=cp), work=4 * c["D"] * pairs, launches=1)
         # DRAM bytes per launch: read + written by the kernel in one profiler capture at batch 1
-        # (50.5 MB + 3.3 MB; K/V re-reads hit L2), times the batch — traffic is per (batch, head).
-        w.update(traffic=53.8e6 * c["B"], traffic_source="ncu dram__bytes_read+write at batch 1, scaled by batch")
+        # (50.5 MB + 2.5 MB; K/V re-reads hit L2), times the batch — traffic is per (batch, head).
+        w.update(traffic=53.0e6 * c["B"], traffic_source="ncu dram__bytes_read+write at batch 1, scaled by batch")
         hQ, hK, hV = (x.cpu().pin_memory() for x in (Q, K, V))
         hO = torch.empty_like(O, device="cpu").pin_memory()
         # End to end from pinned host tensors: every step copies Q, K, V in and O out.  The package's
