@@ -129,6 +129,22 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
   if (mask_flags & TYLO_MASK_DOCUMENT) my_doc = p.doc_q[(size_t)b * p.doc_stride + min(qpos, (int)p.Sq - 1 + p.input_pos)];
   const int n = tr.e - tr.s;
 
+  // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
+  // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
+  // compare per element against the tile-relative start.
+  int row_lo = 0, row_hi = p.Sk - 1;
+  if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) row_hi = min(row_hi, qpos);
+  if (mask_flags & TYLO_MASK_SLIDING) row_lo = max(row_lo, qpos - p.window);
+  if (mask_flags & TYLO_MASK_PREFIX) row_hi = min(row_hi, p.prefix_len - 1);
+  if (mask_flags & TYLO_MASK_PREFIX_LM) row_hi = min(row_hi, max(qpos, p.prefix_len - 1));
+  const bool row_any = row_hi >= row_lo;
+  const unsigned row_span = row_any ? (unsigned)(row_hi - row_lo) : 0u;
+  // soft cap as s * P(s^2) with the constants of the tanh series folded in (see below)
+  const float cap_k1 = p.scale * inv_cap;
+  const float cap_a0 = cap_k1 * p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
+  const float cap_a1 = -0.33333334f * cap_a0 * cap_u, cap_a2 = 0.13333334f * cap_a0 * cap_u * cap_u,
+              cap_a3 = -0.05396825f * cap_a0 * cap_u * cap_u * cap_u;
+
   float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
   bool ok = true;
   for (int i = 0; i < n && ok; ++i) {
@@ -146,6 +162,21 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     const bool tracer = (r == 0);
     if (tracer) TYLO_TRACE(1 + X, i, 0);
     tc_fence_after();
+    // P = 0 for the whole tile: nothing to load, exponentiate or rescale
+    auto pass_empty_tile = [&]() {
+      uint32_t z[32];
+#pragma unroll
+      for (int t = 0; t < 32; ++t) z[t] = 0u;
+      tmem_st32(ts, z); tmem_st32(ts + 32, z);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(SM::P_FULL + X));
+    };
+    if ((mask_flags & TYLO_MASK_DOCUMENT) && doc_uniform && __all_sync(0xffffffffu, ids[0] != my_doc)) {
+      // all 128 keys belong to one document that none of this warp's 32 rows belongs to
+      pass_empty_tile();
+      continue;
+    }
     uint32_t sr[4][32];
 #pragma unroll
     for (int q = 0; q < 4; ++q) tmem_ld32(ts + q * 32, sr[q]);
@@ -175,16 +206,14 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
         for (int t = 0; t < 32; t += 2)
           am[q] = max3(am[q], fabsf(__uint_as_float(sr[q][t])), fabsf(__uint_as_float(sr[q][t + 1])));
       }
-      const float k1 = p.scale * inv_cap;
-      if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * k1 < 0.4f)) {
-        const float k2 = p.cap * kLog2e;
+      if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * cap_k1 < 0.4f)) {
+        // cap*log2e*tanh(x), x = s*k1:  x (1 - x^2/3 + 2x^4/15 - 17x^6/315) = s * (a0 + u (a1 + u (a2 + u a3))), u = s^2
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
-            const float x = __uint_as_float(sr[q][t]) * k1, x2 = x * x;
-            const float th = x * fmaf(x2, fmaf(x2, fmaf(x2, -0.05396825f, 0.13333334f), -0.33333334f), 1.f);
-            sr[q][t] = __float_as_uint(th * k2);
+            const float s = __uint_as_float(sr[q][t]), u = s * s;
+            sr[q][t] = __float_as_uint(s * fmaf(u, fmaf(u, fmaf(u, cap_a3, cap_a2), cap_a1), cap_a0));
           }
         }
         mods_done = true;
@@ -205,21 +234,20 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
         }
       }
     }
+    if (tracer) TYLO_TRACE(1 + X, i, 6);
     if (partial) {
       // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
       // runtime condition makes the compiler wrap every one of the 128 in a convergence barrier.
+      // key kv0 + c is kept iff row_lo <= kv0 + c <= row_hi: (unsigned)(c - rel) <= row_span with
+      // rel = row_lo - kv0; a row that keeps nothing gets a start no column can reach.
+      const int rel = (row_any && row_doc_ok) ? row_lo - kv0 : 0x40000000;
       auto mask_pass = [&](auto with_doc) {
         constexpr bool DOCS = decltype(with_doc)::value;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
-            const int kv = kv0 + q * 32 + t;
-            bool keep = (kv < p.Sk) && row_doc_ok;
-            if (mask_flags & TYLO_MASK_CAUSAL) keep = keep && (qpos >= kv);
-            if (mask_flags & TYLO_MASK_SLIDING) keep = keep && (qpos >= kv) && (qpos <= kv + p.window);
-            if (mask_flags & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
-            if (mask_flags & TYLO_MASK_PREFIX_LM) keep = keep && ((qpos >= kv) || (kv < p.prefix_len));
+            bool keep = (unsigned)(q * 32 + t - rel) <= row_span;
             if (DOCS) {
               const int key_doc = __shfl_sync(0xffffffffu, ids[q], t);   // every lane takes part, masked or not
               keep = keep && (key_doc == my_doc);
@@ -230,6 +258,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       };
       if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
     }
+    if (tracer) TYLO_TRACE(1 + X, i, 7);
     float mxq[4][2];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -246,14 +275,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     if (tracer) TYLO_TRACE(1 + X, i, 2);
     if (__all_sync(0xffffffffu, mx == -INFINITY)) {
       // every pair of this warp's 32 rows is masked in this tile (e.g. keys of another document):
-      // P = 0, nothing to exponentiate or rescale
-      uint32_t z[32];
-#pragma unroll
-      for (int t = 0; t < 32; ++t) z[t] = 0u;
-      tmem_st32(ts, z); tmem_st32(ts + 32, z);
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(SM::P_FULL + X));
+      pass_empty_tile();
       continue;
     }
     // lazy rescaling: move the reference max only when it would otherwise overflow the 2^8 headroom
