@@ -129,34 +129,55 @@ __device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
 // p and the scaled pre-mod score gradient for one element.
 //   s   : raw dot product q.k          dp : dO.v          lse2 / delta : statistics of the query
 // Returns p; ds0 (already multiplied by the qk scale) through the reference.
+//   keep : the pair survives the mask (only read when PARTIAL)     q_minus_kv : position difference (ALiBi)
 template <bool MODDED, bool PARTIAL>
 __device__ __forceinline__ float element(const AttnParams& p, float c, float slope, float inv_cap, float s, float dp,
-                                         float lse2, float delta, int qpos, int kv, bool row_ok, int doc_q, int doc_kv,
-                                         float& ds0) {
+                                         float lse2, float delta, int q_minus_kv, bool keep, float& ds0) {
   float pv, f = p.scale;
   if (MODDED) {
     float s0 = s * p.scale, sm = s0;
     const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
     const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
     if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
-    if (alibi) sm = fmaf(slope, (float)(qpos - kv), sm);
+    if (alibi) sm = fmaf(slope, (float)q_minus_kv, sm);
     if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
     pv = ex2(fmaf(sm, kLog2e, -lse2));
   } else {
     pv = ex2(fmaf(s, c, -lse2));
   }
   if (PARTIAL) {
-    bool keep = row_ok && (kv < p.Sk) && (qpos - p.input_pos < p.Sq);
-    const uint32_t m = p.mask_flags;
-    if (m & TYLO_MASK_CAUSAL) keep = keep && (qpos >= kv);
-    if (m & TYLO_MASK_SLIDING) keep = keep && (qpos >= kv) && (qpos <= kv + p.window);
-    if (m & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
-    if (m & TYLO_MASK_PREFIX_LM) keep = keep && ((qpos >= kv) || (kv < p.prefix_len));
-    if (m & TYLO_MASK_DOCUMENT) keep = keep && (doc_q == doc_kv);
     if (!keep) pv = 0.f;
   }
   ds0 = pv * (dp - delta) * f;
   return pv;
+}
+
+// The streamed positions a row of the owned tile can pair with under every mask term except the
+// document comparison: one interval [lo, hi] of row indices of the streamed tensor (queries for a key
+// row in DKDV mode, keys for a query row in DQ mode); mods.jl:101-167 reduced to bounds.
+__device__ __forceinline__ bool row_interval(const AttnParams& p, bool keys_own, int own_row, int* lo_out, int* hi_out) {
+  const uint32_t m = p.mask_flags;
+  int lo = 0, hi;
+  bool any;
+  if (keys_own) {                      // own row = key kv, streamed = query rows q (position q + input_pos)
+    const int kv = own_row;
+    hi = p.Sq - 1;
+    any = kv < p.Sk;
+    if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) lo = max(lo, kv - p.input_pos);
+    if (m & TYLO_MASK_SLIDING) hi = min(hi, kv + p.window - p.input_pos);
+    if ((m & TYLO_MASK_PREFIX) && kv >= p.prefix_len) any = false;
+    if ((m & TYLO_MASK_PREFIX_LM) && kv >= p.prefix_len) lo = max(lo, kv - p.input_pos);
+  } else {                             // own row = query, streamed = keys
+    const int qpos = own_row + p.input_pos;
+    hi = p.Sk - 1;
+    any = own_row < p.Sq;
+    if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) hi = min(hi, qpos);
+    if (m & TYLO_MASK_SLIDING) lo = max(lo, qpos - p.window);
+    if (m & TYLO_MASK_PREFIX) hi = min(hi, p.prefix_len - 1);
+    if (m & TYLO_MASK_PREFIX_LM) hi = min(hi, max(qpos, p.prefix_len - 1));
+  }
+  *lo_out = lo; *hi_out = hi;
+  return any && hi >= lo;
 }
 
 template <typename T, int D, int MODE>
@@ -369,6 +390,13 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       my_doc = p.doc_kv[(size_t)b * p.doc_stride + min(own_row, p.Sk - 1)];
     }
     const bool row_ok = (MODE == DKDV) ? (own_row < p.Sk) : (own_row < p.Sq);
+    int iv_lo, iv_hi;
+    const bool iv_any = row_interval(p, MODE == DKDV, own_row, &iv_lo, &iv_hi);
+    const unsigned iv_span = iv_any ? (unsigned)(iv_hi - iv_lo) : 0u;
+    // soft cap: tanh(x) ~ x (1 - x^2/3 + 2x^4/15 - 17x^6/315) for |x| < 0.4, written in the raw dot product s (x = s k1)
+    const float cap_k1 = p.scale * inv_cap, cap_k2 = p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
+    const float cap_b1 = -0.33333334f * cap_k1 * cap_u, cap_b2 = 0.13333334f * cap_k1 * cap_u * cap_u,
+                cap_b3 = -0.05396825f * cap_k1 * cap_u * cap_u * cap_u;
 
     bool ok = true;
     for (int n = 0; n < n_iter && ok; ++n) {
@@ -392,6 +420,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_wait_ld();
       if (tracer) TYLO_BTRACE(MODE, 1, n, 1);
       const uint32_t stat_u = sbase + SM::kStats + s * SM::kStatStage;   // lse2[128], delta[128], doc[128]
+      // column j of this warpgroup's half (streamed row tile0 + 64*wg + j) is inside the row's interval
+      // iff (unsigned)(j - rel) <= iv_span; a row that pairs with nothing gets an unreachable start
+      const int rel = iv_any ? iv_lo - tile0 - 64 * wg : 0x40000000;
+      // position difference q - kv of column j: dpos + j in DKDV mode, dpos - j in DQ mode
+      const int dpos = (MODE == DKDV) ? tile0 + 64 * wg + p.input_pos - own_row : own_row + p.input_pos - tile0 - 64 * wg;
 
       // Each warpgroup writes its packed 16-bit columns over the first half of ITS OWN 64 T columns
       // (the MMA addresses the two 32-column pieces separately), so no thread overwrites T values
@@ -415,12 +448,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               float pp[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int col = col0 + e;
-                const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
-                const int kv = (MODE == DKDV) ? own_row : tile0 + col;
+                const int j = q * 32 + t + e;
+                bool keep = (unsigned)(j - rel) <= iv_span;
+                if (PART && has_doc) keep = keep && (doc4[e] == my_doc);
                 float unused;
-                pp[e] = element<false, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), 0.f, lse4[e], 0.f, qpos, kv,
-                                             row_ok, (MODE == DKDV) ? doc4[e] : my_doc, (MODE == DKDV) ? my_doc : doc4[e], unused);
+                pp[e] = element<false, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), 0.f, lse4[e], 0.f, 0,
+                                             keep, unused);
                 sv[q][t + e] = __float_as_uint(pp[e]);
               }
               up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
@@ -464,8 +497,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tc_fence_after();
         tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
         tc_wait_ld();
-        auto run = [&](auto partial_c) {
+        // Soft cap alone with every score of the warp small against the cap (the usual case): tanh is
+        // an odd polynomial with the constants folded in, branch-free, one SFU operation per element.
+        bool fastcap = false;
+        if (p.score_flags == TYLO_SCORE_SOFTCAP) {
+          float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            am0 = fmaxf(am0, fabsf(__uint_as_float(sv[0][t])));
+            am1 = fmaxf(am1, fabsf(__uint_as_float(sv[1][t])));
+          }
+          fastcap = __all_sync(0xffffffffu, fmaxf(am0, am1) * cap_k1 < 0.4f);
+        }
+        auto run = [&](auto partial_c, auto fast_c) {
           constexpr bool PART = decltype(partial_c)::value;
+          constexpr bool FAST = decltype(fast_c)::value;
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             uint32_t up[16], ud[16];
@@ -484,12 +530,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               float pp[4], dd[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int col = col0 + e;
-                const int qpos = ((MODE == DKDV) ? tile0 + col : own_row) + p.input_pos;
-                const int kv = (MODE == DKDV) ? own_row : tile0 + col;
-                pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
-                                            lse4[e], del4[e], qpos, kv, row_ok, (MODE == DKDV) ? doc4[e] : my_doc,
-                                            (MODE == DKDV) ? my_doc : doc4[e], dd[e]);
+                const int j = q * 32 + t + e;
+                bool keep = (unsigned)(j - rel) <= iv_span;
+                if (PART && has_doc) keep = keep && (doc4[e] == my_doc);
+                if (FAST) {
+                  // t = tanh(s k1) = s (b0 + u (b1 + u (b2 + u b3))), u = s^2;  modded score cap*t;  VJP factor scale (1 - t^2)
+                  const float sraw = __uint_as_float(sv[q][t + e]), u = sraw * sraw;
+                  const float th = sraw * fmaf(u, fmaf(u, fmaf(u, cap_b3, cap_b2), cap_b1), cap_k1);
+                  float pv = ex2(fmaf(th, cap_k2, -lse4[e]));
+                  if (PART && !keep) pv = 0.f;
+                  pp[e] = pv;
+                  dd[e] = pv * (__uint_as_float(dv[q][t + e]) - del4[e]) * fmaf(-th * p.scale, th, p.scale);
+                } else {
+                  pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
+                                              lse4[e], del4[e], (MODE == DKDV) ? dpos + j : dpos - j, keep, dd[e]);
+                }
               }
               up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
               ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
@@ -498,7 +553,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
           }
         };
-        if (partial) run(std::true_type{}); else run(std::false_type{});
+        if (fastcap) {
+          if (partial) run(std::true_type{}, std::true_type{}); else run(std::false_type{}, std::true_type{});
+        } else {
+          if (partial) run(std::true_type{}, std::false_type{}); else run(std::false_type{}, std::false_type{});
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(SM::U1_FULL));
