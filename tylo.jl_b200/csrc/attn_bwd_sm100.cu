@@ -60,7 +60,7 @@ template <int D> struct Smem {
   static constexpr int kX = 0;                               // two stationary tiles
   static constexpr int kY = 2 * kTile;                       // ring of (Y1, Y2) pairs
   static constexpr int kStats = kY + kStages * 2 * kTile;    // per stage: lse2[128], delta[128], doc[128]
-  static constexpr int kStatStage = 3 * BT * 4;
+  static constexpr int kStatStage = 3 * BT * 4 + 16;         // + smallest / largest document id of the tile
   static constexpr int kBars = kStats + kStages * kStatStage;
   static constexpr int X_FULL = 0, Y_FULL = 1, Y_EMPTY = Y_FULL + kStages, STAT_FULL = Y_EMPTY + kStages,
                        T1_FULL = STAT_FULL + kStages, T2_FULL = T1_FULL + 1, U1_FULL = T2_FULL + 1, U2_FULL = U1_FULL + 1, DONE = U2_FULL + 1,
@@ -280,17 +280,32 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         // statistics / document ids of the streamed tile's positions
         float* slse = stat(s, 0); float* sdel = stat(s, 1); int* sdoc = reinterpret_cast<int*>(stat(s, 2));
+        int dmin = 0x7fffffff, dmax = (int)0x80000000;
         for (int idx = lane; idx < BT; idx += 32) {
           const int row = row0 + idx;
+          int doc = 0;
           if (MODE == DKDV) {
             const bool valid = row < p.Sq;
             const size_t si = (size_t)(b * p.H + h0 + g) * p.Sq + (valid ? row : 0);
             slse[idx] = valid ? lse2g[si] : INFINITY;
-            sdel[idx] = valid ? deltag[si] : 0.f;
-            sdoc[idx] = (p.mask_flags & TYLO_MASK_DOCUMENT) ? p.doc_q[(size_t)b * p.doc_stride + min(row, p.Sq - 1) + p.input_pos] : 0;
+            // without score mods the element pass wants scale * Delta (one fused multiply-add per element)
+            sdel[idx] = valid ? deltag[si] * (p.score_flags != 0 ? 1.f : p.scale) : 0.f;
+            if (p.mask_flags & TYLO_MASK_DOCUMENT) doc = p.doc_q[(size_t)b * p.doc_stride + min(row, p.Sq - 1) + p.input_pos];
           } else {
-            sdoc[idx] = (p.mask_flags & TYLO_MASK_DOCUMENT) ? p.doc_kv[(size_t)b * p.doc_stride + min(row, p.Sk - 1)] : 0;
+            if (p.mask_flags & TYLO_MASK_DOCUMENT) doc = p.doc_kv[(size_t)b * p.doc_stride + min(row, p.Sk - 1)];
           }
+          sdoc[idx] = doc;
+          dmin = min(dmin, doc); dmax = max(dmax, doc);
+        }
+        if (p.mask_flags & TYLO_MASK_DOCUMENT) {
+          // smallest and largest id of the tile: equal means one document, which lets the compute
+          // warps drop the per-element comparison or skip the tile
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            dmin = min(dmin, __shfl_xor_sync(0xffffffffu, dmin, o));
+            dmax = max(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
+          }
+          if (lane == 0) { sdoc[BT] = dmin; sdoc[BT + 1] = dmax; }
         }
         mbar_arrive(bar(SM::STAT_FULL + s));
       }
@@ -382,7 +397,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (MODE == DQ) {
       if (own_row < p.Sq) {
         const size_t si = (size_t)(b * p.H + h0) * p.Sq + own_row;
-        my_lse = lse2g[si]; my_delta = deltag[si];
+        my_lse = lse2g[si]; my_delta = deltag[si] * (modded ? 1.f : p.scale);
       }
       if (has_doc) my_doc = p.doc_q[(size_t)b * p.doc_stride + min(own_row, p.Sq - 1) + p.input_pos];
       if (p.score_flags & TYLO_SCORE_ALIBI) slope = p.slopes[h0];
@@ -405,7 +420,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const int tile0 = (it_lo + ((MODE == DKDV) ? n % it_n : n)) * BT;
       if (MODE == DKDV && (p.score_flags & TYLO_SCORE_ALIBI)) slope = p.slopes[h0 + g];
       const int qa = (MODE == DKDV) ? tile0 : own0, ka = (MODE == DKDV) ? own0 : tile0;
-      bool partial = (ka + BT > p.Sk) || (qa + BT > p.Sq) || has_doc || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
+      bool partial = (ka + BT > p.Sk) || (qa + BT > p.Sq) || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
       if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) partial = partial || (ka + BT - 1 > qa + p.input_pos);
       if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
 
@@ -415,6 +430,36 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const bool tracer = (r == 0 && wg == 0);
       if (tracer) TYLO_BTRACE(MODE, 1, n, 0);
       tc_fence_after();
+      // Document mask: the producer left the smallest and largest id of the streamed tile.  One document
+      // that none of this warp's 32 rows belongs to: P = dS = 0 for the warp's rows, nothing to compute.
+      // One document that all of them belong to: no per-element comparison.
+      bool doc_cmp = false;
+      if (has_doc) {
+        const int* sd = reinterpret_cast<const int*>(smem + SM::kStats + s * SM::kStatStage + 2 * BT * 4);
+        const int dmin = sd[BT], dmax = sd[BT + 1];
+        const bool one_doc = dmin == dmax;
+        if (one_doc && __all_sync(0xffffffffu, my_doc != dmin)) {
+          uint32_t z[16];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) z[t] = 0u;
+          if (MODE == DKDV) {
+            tmem_st16x(tmem + lane_off + 64 * wg, z); tmem_st16x(tmem + lane_off + 64 * wg + 16, z);
+            tc_wait_st();
+          }
+          tc_fence_before();
+          mbar_arrive(bar(SM::U1_FULL));
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 303));
+          if (!ok) break;
+          tc_fence_after();
+          tmem_st16x(tmem + 128 + lane_off + 64 * wg, z); tmem_st16x(tmem + 128 + lane_off + 64 * wg + 16, z);
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(SM::U2_FULL));
+          continue;
+        }
+        doc_cmp = !(one_doc && __all_sync(0xffffffffu, my_doc == dmin));
+        partial = partial || doc_cmp;
+      }
       uint32_t sv[2][32], dv[2][32];
       tmem_ld32(tmem + lane_off + 64 * wg, sv[0]); tmem_ld32(tmem + lane_off + 64 * wg + 32, sv[1]);
       tc_wait_ld();
@@ -450,7 +495,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               for (int e = 0; e < 4; ++e) {
                 const int j = q * 32 + t + e;
                 bool keep = (unsigned)(j - rel) <= iv_span;
-                if (PART && has_doc) keep = keep && (doc4[e] == my_doc);
+                if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
                 float unused;
                 pp[e] = element<false, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), 0.f, lse4[e], 0.f, 0,
                                              keep, unused);
@@ -485,7 +530,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             float dd[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              dd[e] = __uint_as_float(sv[q][t + e]) * (__uint_as_float(dv[q][t + e]) - del4[e]) * p.scale;
+              dd[e] = __uint_as_float(sv[q][t + e]) * fmaf(__uint_as_float(dv[q][t + e]), p.scale, -del4[e]);   // del4 = scale * Delta
             ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
           }
           tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
@@ -532,7 +577,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               for (int e = 0; e < 4; ++e) {
                 const int j = q * 32 + t + e;
                 bool keep = (unsigned)(j - rel) <= iv_span;
-                if (PART && has_doc) keep = keep && (doc4[e] == my_doc);
+                if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
                 if (FAST) {
                   // t = tanh(s k1) = s (b0 + u (b1 + u (b2 + u b3))), u = s^2;  modded score cap*t;  VJP factor scale (1 - t^2)
                   const float sraw = __uint_as_float(sv[q][t + e]), u = sraw * sraw;
