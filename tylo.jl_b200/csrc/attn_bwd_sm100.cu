@@ -129,10 +129,11 @@ __device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
 // p and the scaled pre-mod score gradient for one element.
 //   s   : raw dot product q.k          dp : dO.v          lse2 / delta : statistics of the query
 // Returns p; ds0 (already multiplied by the qk scale) through the reference.
+//   nlse, ndelta : the statistics NEGATED (so that they enter as addends of fused multiply-adds)
 //   keep : the pair survives the mask (only read when PARTIAL)     q_minus_kv : position difference (ALiBi)
 template <bool MODDED, bool PARTIAL>
 __device__ __forceinline__ float element(const AttnParams& p, float c, float slope, float inv_cap, float s, float dp,
-                                         float lse2, float delta, int q_minus_kv, bool keep, float& ds0) {
+                                         float nlse, float ndelta, int q_minus_kv, bool keep, float& ds0) {
   float pv, f = p.scale;
   if (MODDED) {
     float s0 = s * p.scale, sm = s0;
@@ -141,14 +142,14 @@ __device__ __forceinline__ float element(const AttnParams& p, float c, float slo
     if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
     if (alibi) sm = fmaf(slope, (float)q_minus_kv, sm);
     if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
-    pv = ex2(fmaf(sm, kLog2e, -lse2));
+    pv = ex2(fmaf(sm, kLog2e, nlse));
   } else {
-    pv = ex2(fmaf(s, c, -lse2));
+    pv = ex2(fmaf(s, c, nlse));
   }
   if (PARTIAL) {
     if (!keep) pv = 0.f;
   }
-  ds0 = pv * (dp - delta) * f;
+  ds0 = pv * (dp + ndelta) * f;
   return pv;
 }
 
@@ -287,9 +288,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (MODE == DKDV) {
             const bool valid = row < p.Sq;
             const size_t si = (size_t)(b * p.H + h0 + g) * p.Sq + (valid ? row : 0);
-            slse[idx] = valid ? lse2g[si] : INFINITY;
-            // without score mods the element pass wants scale * Delta (one fused multiply-add per element)
-            sdel[idx] = valid ? deltag[si] * (p.score_flags != 0 ? 1.f : p.scale) : 0.f;
+            // Both statistics are staged NEGATED, as the addends of the element pass's fused multiply-adds:
+            // -lse2, and -Delta (with score mods) or -scale * Delta (without).
+            slse[idx] = valid ? -lse2g[si] : -INFINITY;
+            sdel[idx] = valid ? -deltag[si] * (p.score_flags != 0 ? 1.f : p.scale) : 0.f;
             if (p.mask_flags & TYLO_MASK_DOCUMENT) doc = p.doc_q[(size_t)b * p.doc_stride + min(row, p.Sq - 1) + p.input_pos];
           } else {
             if (p.mask_flags & TYLO_MASK_DOCUMENT) doc = p.doc_kv[(size_t)b * p.doc_stride + min(row, p.Sk - 1)];
@@ -392,12 +394,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const float inv_cap = 1.f / p.cap;
     const bool has_doc = p.mask_flags & TYLO_MASK_DOCUMENT;
     // per-thread constants of the owned row
-    float my_lse = INFINITY, my_delta = 0.f, slope = 0.f;
+    float my_lse = -INFINITY, my_delta = 0.f, slope = 0.f;   // negated, like the staged per-column statistics
     int my_doc = 0;
     if (MODE == DQ) {
       if (own_row < p.Sq) {
         const size_t si = (size_t)(b * p.H + h0) * p.Sq + own_row;
-        my_lse = lse2g[si]; my_delta = deltag[si] * (modded ? 1.f : p.scale);
+        my_lse = -lse2g[si]; my_delta = -deltag[si] * (modded ? 1.f : p.scale);
       }
       if (has_doc) my_doc = p.doc_q[(size_t)b * p.doc_stride + min(own_row, p.Sq - 1) + p.input_pos];
       if (p.score_flags & TYLO_SCORE_ALIBI) slope = p.slopes[h0];
@@ -412,6 +414,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const float cap_k1 = p.scale * inv_cap, cap_k2 = p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
     const float cap_b1 = -0.33333334f * cap_k1 * cap_u, cap_b2 = 0.13333334f * cap_k1 * cap_u * cap_u,
                 cap_b3 = -0.05396825f * cap_k1 * cap_u * cap_u * cap_u;
+    // the same constants as packed pairs for the two-columns-per-instruction forms
+    const uint64_t c2 = pack_f32x2(c, c), scale2 = pack_f32x2(p.scale, p.scale), nscale2 = pack_f32x2(-p.scale, -p.scale);
+    const uint64_t cb0_2 = pack_f32x2(cap_k1, cap_k1), cb1_2 = pack_f32x2(cap_b1, cap_b1), cb2_2 = pack_f32x2(cap_b2, cap_b2),
+                   cb3_2 = pack_f32x2(cap_b3, cap_b3), ck2_2 = pack_f32x2(cap_k2, cap_k2);
 
     bool ok = true;
     for (int n = 0; n < n_iter && ok; ++n) {
@@ -492,13 +498,20 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               const int doc4[4] = {d0, d1, d2, d3};
               float pp[4];
 #pragma unroll
+              for (int e = 0; e < 4; e += 2) {     // exponent arguments two at a time: s c + (-lse2)
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[q][t + e]), __uint_as_float(sv[q][t + e + 1])), c2,
+                                       pack_f32x2(lse4[e], lse4[e + 1])), x0, x1);
+                pp[e] = ex2(x0); pp[e + 1] = ex2(x1);
+              }
+#pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int j = q * 32 + t + e;
-                bool keep = (unsigned)(j - rel) <= iv_span;
-                if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
-                float unused;
-                pp[e] = element<false, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), 0.f, lse4[e], 0.f, 0,
-                                             keep, unused);
+                if (PART) {
+                  const int j = q * 32 + t + e;
+                  bool keep = (unsigned)(j - rel) <= iv_span;
+                  if (doc_cmp) keep = keep && (doc4[e] == my_doc);
+                  if (!keep) pp[e] = 0.f;
+                }
                 sv[q][t + e] = __float_as_uint(pp[e]);
               }
               up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
@@ -529,8 +542,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const float del4[4] = {e0, e1, e2, e3};
             float dd[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              dd[e] = __uint_as_float(sv[q][t + e]) * fmaf(__uint_as_float(dv[q][t + e]), p.scale, -del4[e]);   // del4 = scale * Delta
+            for (int e = 0; e < 4; e += 2) {      // p (dp scale + (-scale Delta)), two at a time
+              const uint64_t g2 = fma_f32x2(pack_f32x2(__uint_as_float(dv[q][t + e]), __uint_as_float(dv[q][t + e + 1])), scale2,
+                                            pack_f32x2(del4[e], del4[e + 1]));
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(sv[q][t + e]), __uint_as_float(sv[q][t + e + 1])), g2),
+                           dd[e], dd[e + 1]);
+            }
             ud[t / 2] = pack16<T>(dd[0], dd[1]); ud[t / 2 + 1] = pack16<T>(dd[2], dd[3]);
           }
           tmem_st16x(tmem + 128 + lane_off + 64 * wg + q * 16, ud);
@@ -573,20 +590,36 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               const float lse4[4] = {l0, l1, l2, l3}, del4[4] = {e0, e1, e2, e3};
               const int doc4[4] = {d0, d1, d2, d3};
               float pp[4], dd[4];
+              if (FAST) {
+                // t = tanh(s k1) = s (b0 + u (b1 + u (b2 + u b3))), u = s^2;  modded score cap*t;  VJP factor
+                // scale (1 - t^2); two columns per instruction
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int j = q * 32 + t + e;
-                bool keep = (unsigned)(j - rel) <= iv_span;
-                if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
-                if (FAST) {
-                  // t = tanh(s k1) = s (b0 + u (b1 + u (b2 + u b3))), u = s^2;  modded score cap*t;  VJP factor scale (1 - t^2)
-                  const float sraw = __uint_as_float(sv[q][t + e]), u = sraw * sraw;
-                  const float th = sraw * fmaf(u, fmaf(u, fmaf(u, cap_b3, cap_b2), cap_b1), cap_k1);
-                  float pv = ex2(fmaf(th, cap_k2, -lse4[e]));
-                  if (PART && !keep) pv = 0.f;
-                  pp[e] = pv;
-                  dd[e] = pv * (__uint_as_float(dv[q][t + e]) - del4[e]) * fmaf(-th * p.scale, th, p.scale);
-                } else {
+                for (int e = 0; e < 4; e += 2) {
+                  const uint64_t s2 = pack_f32x2(__uint_as_float(sv[q][t + e]), __uint_as_float(sv[q][t + e + 1]));
+                  const uint64_t u2 = mul_f32x2(s2, s2);
+                  const uint64_t th2 = mul_f32x2(s2, fma_f32x2(u2, fma_f32x2(u2, fma_f32x2(u2, cb3_2, cb2_2), cb1_2), cb0_2));
+                  float x0, x1;
+                  unpack_f32x2(fma_f32x2(th2, ck2_2, pack_f32x2(lse4[e], lse4[e + 1])), x0, x1);
+                  float p0 = ex2(x0), p1 = ex2(x1);
+                  if (PART) {
+                    const int j = q * 32 + t + e;
+                    bool k0 = (unsigned)(j - rel) <= iv_span, k1 = (unsigned)(j + 1 - rel) <= iv_span;
+                    if (doc_cmp) { k0 = k0 && (doc4[e] == my_doc); k1 = k1 && (doc4[e + 1] == my_doc); }
+                    if (!k0) p0 = 0.f;
+                    if (!k1) p1 = 0.f;
+                  }
+                  pp[e] = p0; pp[e + 1] = p1;
+                  const uint64_t f2 = fma_f32x2(mul_f32x2(th2, nscale2), th2, scale2);          // scale - scale t^2
+                  const uint64_t g2 = add_f32x2(pack_f32x2(__uint_as_float(dv[q][t + e]), __uint_as_float(dv[q][t + e + 1])),
+                                                pack_f32x2(del4[e], del4[e + 1]));                 // dp + (-Delta)
+                  unpack_f32x2(mul_f32x2(mul_f32x2(pack_f32x2(p0, p1), g2), f2), dd[e], dd[e + 1]);
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int j = q * 32 + t + e;
+                  bool keep = (unsigned)(j - rel) <= iv_span;
+                  if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
                   pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
                                               lse4[e], del4[e], (MODE == DKDV) ? dpos + j : dpos - j, keep, dd[e]);
                 }

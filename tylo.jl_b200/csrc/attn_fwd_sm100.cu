@@ -83,6 +83,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+#ifndef TYLO_FWD_F32X2
+#define TYLO_FWD_F32X2 1   // 0: scalar fp32 in the element loops (A/B aid)
+#endif
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -208,6 +211,21 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       }
       if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * cap_k1 < 0.4f)) {
         // cap*log2e*tanh(x), x = s*k1:  x (1 - x^2/3 + 2x^4/15 - 17x^6/315) = s * (a0 + u (a1 + u (a2 + u a3))), u = s^2
+#if TYLO_FWD_F32X2
+        const uint64_t a0 = pack_f32x2(cap_a0, cap_a0), a1 = pack_f32x2(cap_a1, cap_a1), a2 = pack_f32x2(cap_a2, cap_a2),
+                       a3 = pack_f32x2(cap_a3, cap_a3);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int t = 0; t < 32; t += 2) {
+            const uint64_t s2 = pack_f32x2(__uint_as_float(sr[q][t]), __uint_as_float(sr[q][t + 1]));
+            const uint64_t u2 = mul_f32x2(s2, s2);
+            float y0, y1;
+            unpack_f32x2(mul_f32x2(s2, fma_f32x2(u2, fma_f32x2(u2, fma_f32x2(u2, a3, a2), a1), a0)), y0, y1);
+            sr[q][t] = __float_as_uint(y0); sr[q][t + 1] = __float_as_uint(y1);
+          }
+        }
+#else
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
@@ -216,6 +234,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
             sr[q][t] = __float_as_uint(s * fmaf(u, fmaf(u, fmaf(u, cap_a3, cap_a2), cap_a1), cap_a0));
           }
         }
+#endif
         mods_done = true;
       }
     }
@@ -303,16 +322,32 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     if (tracer) TYLO_TRACE(1 + X, i, 3);
     const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
     float lsq[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+#if TYLO_FWD_F32X2
+    // Two scores per instruction on the FMA pipe: fma.rn.f32x2 for the exponent arguments and
+    // add.rn.f32x2 for the running row sums (register pairs, sm_100 packed fp32).
+    const uint64_t c2 = pack_f32x2(c, c), mc2 = pack_f32x2(-mc, -mc);
+    uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
+#endif
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t pk[16];
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
+#if TYLO_FWD_F32X2
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[q][2 * t]), __uint_as_float(sr[q][2 * t + 1])), c2, mc2), x0, x1);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        ls2[q] = add_f32x2(ls2[q], pack_f32x2(p0, p1));
+#else
         const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q][2 * t]), c, -mc));
         const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q][2 * t + 1]), c, -mc));
         lsq[q][0] += p0; lsq[q][1] += p1;
+#endif
         pk[t] = pack_pair<T>(p0, p1);
       }
+#if TYLO_FWD_F32X2
+      unpack_f32x2(ls2[q], lsq[q][0], lsq[q][1]);
+#endif
       // 16 columns of packed pairs = 32 probabilities
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
