@@ -71,3 +71,14 @@ def test_bias_rejections(tylo):
     both_sides = tylo.BiasScore(torch.zeros(1, 1, 64, 64, device="cuda")) @ (tylo.SoftCapScore(5.0) @ tylo.AliBiScore(slopes))
     with pytest.raises(tylo.TyloError):
         tylo.flex_attention(Q, K, V, score_mod=both_sides)
+
+
+def test_score_chain_mapping(tylo):
+    """Composed score mods -> descriptor flags: additive mods on either side of the soft cap."""
+    bias = torch.zeros(1, 1, 4, 4, device="cuda")
+    slopes = torch.ones(2, device="cuda")
+    keep = []
+    d = tylo._score_desc(tylo.SoftCapScore(5.0) @ (tylo.BiasScore(bias) @ tylo.AliBiScore(slopes)), None, keep)
+    assert d.flags == tylo.SCORE_SOFTCAP | tylo.SCORE_BIAS | tylo.SCORE_ALIBI and (d.bias_batch, d.bias_heads) == (1, 1)
+    d = tylo._score_desc(tylo.BiasScore(bias) @ tylo.SoftCapScore(5.0), None, keep)
+    assert d.flags == tylo.SCORE_SOFTCAP | tylo.SCORE_BIAS | tylo.SCORE_SOFTCAP_FIRST
