@@ -197,6 +197,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   auto stat = [&](int s, int which) { return reinterpret_cast<float*>(smem + SM::kStats + s * SM::kStatStage + which * BT * 4); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // dK/dV kernel: once its last CTAs are resident, the dQ kernel behind it may start filling idle SMs
+  if (MODE == DKDV) asm volatile("griddepcontrol.launch_dependents;");
 
   // ---- what this CTA owns and which tiles it streams
   int b, h0, hk, own0;       // own0: first row (key or query) of the owned tile
@@ -769,7 +771,18 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
     auto kern = attn_bwd_sm100_kernel<T, D, DQ>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
     const long long grid = (long long)((p.Sq + BT - 1) / BT) * p.H * p.B;
-    kern<<<(unsigned)grid, kThreads, Smem<D>::kDynamic, st>>>(mq, mk, mv, mdo, (T*)dQ, nullptr, lse2, Delta, p);
+    // The dQ kernel reads nothing the dK/dV kernel writes (both depend only on the inputs and on the prep
+    // kernel, which finished before the dK/dV kernel started).  It is launched as a programmatic
+    // dependent of the dK/dV kernel and never waits on it, so its CTAs fill the SMs that the last wave
+    // of the dK/dV kernel leaves idle.  Work submitted to the stream afterwards still waits for both.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = Smem<D>::kDynamic; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    TYLO_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mdo, (T*)dQ, (T*)nullptr, (const float*)lse2,
+                                    (const float*)Delta, p));
     if (int32_t rc = check_launch("attn_bwd_sm100<dq>")) return rc;
   }
   return TYLO_OK;
