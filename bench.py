@@ -263,21 +263,50 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
 
 
 def make_rowwise(t, torch, seed, kind):
+    """Row kernels, forward (`softmax`, `rms_norm`, `layer_norm`) and backward (`*_bwd`).  Algorithmic bytes:
+    forward one read + one write of the matrix; backward two reads (the saved tensor and the incoming
+    gradient) + one write, 2 bytes each; parameter vectors and per-group partials are not counted."""
     g = torch.Generator(device="cuda").manual_seed(seed)
-    if kind == "softmax":
+    bwd = kind.endswith("_bwd")
+    base = kind[:-4] if bwd else kind
+    launches = 1
+    if base == "softmax":
         N, M = ROWS["softmax"]
         X = (2 * torch.randn(N, M, device="cuda", generator=g)).to(torch.bfloat16)
         Y = torch.empty_like(X)
         step = lambda: t.softmax_(Y, X)
+        if bwd:
+            step()
+            dY = torch.randn(N, M, device="cuda", generator=g).to(torch.bfloat16)
+            Yd, Xd = t.Duplicated(Y, dY), t.Duplicated(X)
+            step = lambda: t.grad_softmax_(Yd, Xd)
     else:
         N, M = ROWS["norm"]
         X = torch.randn(N, M, device="cuda", generator=g).to(torch.bfloat16)
         W = (1 + 0.02 * torch.randn(M, device="cuda", generator=g)).to(torch.bfloat16)
         Bv = (0.02 * torch.randn(M, device="cuda", generator=g)).to(torch.bfloat16)
         Y = torch.empty_like(X)
-        step = (lambda: t.rms_norm_(Y, X, W, eps=1e-6)) if kind == "rms_norm" else (lambda: t.layer_norm_(Y, X, W, Bv, eps=1e-6))
-    return dict(name=kind, unit="GB/s", bound="hbm", scale=1e-9, launches=1, step=step, work=N * M * 4,
-                config=dict(workload=f"{kind} forward, bf16", rows=N, row_len=M))
+        if base == "rms_norm":
+            cp = t.allocate_checkpoints_rms_norm(X, W)
+            step = lambda: t.rms_norm_(Y, X, W, eps=1e-6, checkpoints=cp if bwd else None)
+        else:
+            cp = t.allocate_checkpoints_layer_norm(X, W, Bv)
+            step = lambda: t.layer_norm_(Y, X, W, Bv, eps=1e-6, checkpoints=cp if bwd else None)
+        if bwd:
+            step()
+            dY = torch.randn(N, M, device="cuda", generator=g).to(torch.bfloat16)
+            Yd, Xd, Wd = t.Duplicated(Y, dY), t.Duplicated(X), t.Duplicated(W)
+            launches = 2
+            if base == "rms_norm":
+                sc = t.allocate_scratchspace_grad_rms_norm(X, W)
+                step = lambda: t.grad_rms_norm_(Yd, Xd, Wd, checkpoints=cp, scratch=sc)
+            else:
+                Bd = t.Duplicated(Bv)
+                sc = t.allocate_scratchspace_grad_layer_norm(X, W, Bv)
+                step = lambda: t.grad_layer_norm_(Yd, Xd, Wd, Bd, checkpoints=cp, scratch=sc)
+    return dict(name=kind, unit="GB/s", bound="hbm", scale=1e-9, launches=launches, step=step,
+                work=N * M * (6 if bwd else 4),
+                config=dict(workload=f"{base} {'backward' if bwd else 'forward'}, bf16", rows=N, row_len=M))
 
 
 def make_fp32(t, torch, seed):
@@ -413,6 +442,9 @@ def main():
         "rms_norm": lambda: make_rowwise(t, torch, 1, "rms_norm"),
         "layer_norm": lambda: make_rowwise(t, torch, 1, "layer_norm"),
         "softmax": lambda: make_rowwise(t, torch, 1, "softmax"),
+        "rms_norm_bwd": lambda: make_rowwise(t, torch, 1, "rms_norm_bwd"),
+        "layer_norm_bwd": lambda: make_rowwise(t, torch, 1, "layer_norm_bwd"),
+        "softmax_bwd": lambda: make_rowwise(t, torch, 1, "softmax_bwd"),
         "mha_fp32": lambda: make_fp32(t, torch, 0),
     }
 

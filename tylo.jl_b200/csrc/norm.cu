@@ -304,6 +304,90 @@ norm_bwd_kernel(T* __restrict__ dX, float* __restrict__ dWp, float* __restrict__
   }
 }
 
+// backward, streaming form for rows of exactly THREADS packets (one 16-byte packet of X and of dY per
+// thread): the per-thread state is a handful of registers, so the packets of the next TWO rows are
+// already in flight while the current row is reduced — the HBM stream never waits for a reduction.
+// One barrier per row (the reduction scratch is double-buffered).
+template <typename T, int THREADS, bool LAYER>
+__global__ void __launch_bounds__(THREADS)
+norm_bwd_stream_kernel(T* __restrict__ dX, float* __restrict__ dWp, float* __restrict__ dBp,
+                       const T* __restrict__ dY, const T* __restrict__ X, const T* __restrict__ W,
+                       const float* __restrict__ Mean, const float* __restrict__ Rstd,
+                       int M, int64_t N, float offset) {
+  constexpr int VEC = Elem<T>::kVec;
+  constexpr int kWarps = THREADS / 32;
+  __shared__ float red[2][64];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t col = (size_t)threadIdx.x * VEC;
+  const float inv_m = 1.0f / (float)M;
+  float g[VEC], dw[VEC], db[VEC];
+  ld_param(W + col).unpack(g);
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    if constexpr (!LAYER) g[j] += offset;
+    dw[j] = 0.f; db[j] = 0.f;
+  }
+  const int64_t stride = gridDim.x;
+  Pack<T> x0, d0, x1, d1, x2, d2;
+  float r0 = 0.f, r1 = 0.f, r2 = 0.f, m0 = 0.f, m1 = 0.f, m2 = 0.f;
+  auto fetch = [&](int64_t r, Pack<T>& x, Pack<T>& d, float& rs, float& mn) {
+    if (r < N) {
+      x.raw = ld_stream(X + r * M + col); d.raw = ld_stream(dY + r * M + col);
+      rs = Rstd[r];
+      mn = LAYER ? Mean[r] : 0.f;
+    }
+  };
+  int64_t row = blockIdx.x;
+  // rows in flight behind the current one: two for RMSNorm, one for LayerNorm (its extra accumulators
+  // and statistics would otherwise push the 1024-thread CTA past 64 registers per thread)
+  fetch(row, x0, d0, r0, m0);
+  if constexpr (!LAYER) fetch(row + stride, x1, d1, r1, m1);
+  for (int par = 0; row < N; row += stride, par ^= 1) {
+    if constexpr (LAYER) fetch(row + stride, x1, d1, r1, m1);
+    else fetch(row + 2 * stride, x2, d2, r2, m2);
+    float s1 = 0.f, s2 = 0.f;
+    {
+      float xf[VEC], df[VEC];
+      x0.unpack(xf); d0.unpack(df);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float gd = g[j] * df[j];
+        s1 += (xf[j] - m0) * r0 * gd;
+        if constexpr (LAYER) s2 += gd;
+      }
+    }
+    s1 = warp_reduce(s1, SumOp());
+    if constexpr (LAYER) s2 = warp_reduce(s2, SumOp());
+    if (lane == 0) { red[par][warp] = s1; red[par][32 + warp] = s2; }
+    __syncthreads();
+    s1 = warp_reduce(lane < kWarps ? red[par][lane] : 0.f, SumOp());
+    if constexpr (LAYER) s2 = warp_reduce(lane < kWarps ? red[par][32 + lane] : 0.f, SumOp());
+    const float c1 = s1 * inv_m, c2 = LAYER ? s2 * inv_m : 0.f;
+    // the packets are unpacked again rather than kept as fp32 across the barrier (registers)
+    float xf[VEC], df[VEC], o[VEC];
+    x0.unpack(xf); d0.unpack(df);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float xhat = (xf[j] - m0) * r0;
+      o[j] = (g[j] * df[j] - (xhat * c1 + c2)) * r0;     // same formulas as norm_bwd_kernel
+      dw[j] += df[j] * xhat;
+      if constexpr (LAYER) db[j] += df[j];
+    }
+    Pack<T> out; out.pack(o);
+    st_stream(dX + row * M + col, out.raw);
+    x0 = x1; d0 = d1; r0 = r1; m0 = m1;
+    if constexpr (!LAYER) { x1 = x2; d1 = d2; r1 = r2; m1 = m2; }
+  }
+  float4* pw = reinterpret_cast<float4*>(dWp + (size_t)blockIdx.x * M + col);
+#pragma unroll
+  for (int j = 0; j < VEC; j += 4) pw[j / 4] = make_float4(dw[j], dw[j + 1], dw[j + 2], dw[j + 3]);
+  if constexpr (LAYER) {
+    float4* pb = reinterpret_cast<float4*>(dBp + (size_t)blockIdx.x * M + col);
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) pb[j / 4] = make_float4(db[j], db[j + 1], db[j + 2], db[j + 3]);
+  }
+}
+
 // backward for any M / alignment: the CTA's partial row is accumulated in global memory
 // (the CTA is its only writer).
 template <typename T, bool LAYER>
@@ -393,7 +477,19 @@ static int32_t norm_bwd_launch(void* dX, void* dW, void* dB, const void* dY, con
                                cudaStream_t st) {
   constexpr int VEC = Elem<T>::kVec;
   RowShape shape;
-  const unsigned grid = (unsigned)(n_groups < N ? n_groups : N);
+  unsigned grid = (unsigned)(n_groups < N ? n_groups : N);
+  const int64_t nvec = M % VEC == 0 ? M / VEC : 0;
+  if (nvec == 1024 || nvec == 512) {
+    // rows of exactly one packet per thread: the streaming form, one CTA per SM (two at 512 threads)
+    const unsigned walkers = (unsigned)sm_count() * (nvec == 1024 ? 1u : 2u);
+    if (grid > walkers) grid = walkers;
+    if (nvec == 1024)
+      norm_bwd_stream_kernel<T, 1024, LAYER><<<grid, 1024, 0, st>>>(
+          (T*)dX, dWp, dBp, (const T*)dY, (const T*)X, (const T*)W, Mean, Rstd, (int)M, N, offset);
+    else
+      norm_bwd_stream_kernel<T, 512, LAYER><<<grid, 512, 0, st>>>(
+          (T*)dX, dWp, dBp, (const T*)dY, (const T*)X, (const T*)W, Mean, Rstd, (int)M, N, offset);
+  } else
   // register-resident shapes only while the per-thread dW/dB accumulators fit without spilling
   if (M % VEC == 0 && M / VEC <= 1024 && pick_row_shape(M / VEC, 4, &shape)) {
 #define TYLO_BWD_LAUNCH(THREADS, ITERS)                                                             \
