@@ -11,6 +11,11 @@
 // (the reference serialises the groups on a global spin-lock: rms_norm.jl:68-78,
 // layer_norm.jl:102-116).
 #include "rowwise.cuh"
+#include "sm100_ptx.cuh"
+
+#ifndef TYLO_NORM_F32X2
+#define TYLO_NORM_F32X2 1   // 0: scalar fp32 in the forward element loops (A/B aid)
+#endif
 
 namespace tylo {
 
@@ -116,6 +121,36 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
     // Per-thread mean and centred second moment from the registers, then ONE reduction round that
     // merges (count, mean, M2) triples (Chan et al.): centred accuracy without a second barrier.
     float cnt = 0.f, s = 0.f;
+#if TYLO_NORM_F32X2
+    // two elements per instruction (packed fp32 pairs): the kernel is close enough to the issue limit
+    // for the instruction count to show in its bandwidth
+    uint64_t s2 = 0ull;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      if (i * THREADS + (int)threadIdx.x < nvec) {
+        float f[VEC]; x.p[i].unpack(f);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) s2 = sm100::add_f32x2(s2, sm100::pack_f32x2(f[j], f[j + 1]));
+        cnt += (float)VEC;
+      }
+    }
+    { float a, b; sm100::unpack_f32x2(s2, a, b); s = a + b; }
+    float mu = cnt > 0.f ? s / cnt : 0.f, m2 = 0.f;
+    const uint64_t nmu2 = sm100::pack_f32x2(-mu, -mu);
+    uint64_t q2 = 0ull;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      if (i * THREADS + (int)threadIdx.x < nvec) {
+        float f[VEC]; x.p[i].unpack(f);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) {
+          const uint64_t c2 = sm100::add_f32x2(sm100::pack_f32x2(f[j], f[j + 1]), nmu2);
+          q2 = sm100::fma_f32x2(c2, c2, q2);
+        }
+      }
+    }
+    { float a, b; sm100::unpack_f32x2(q2, a, b); m2 = a + b; }
+#else
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       if (i * THREADS + (int)threadIdx.x < nvec) {
@@ -134,16 +169,31 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
         for (int j = 0; j < VEC; ++j) { const float c = f[j] - mu; m2 += c * c; }
       }
     }
+#endif
     if (nvec == THREADS * ITERS) welford_block_equal<THREADS>((float)(ITERS * VEC), mu, m2, wred);
     else welford_block<THREADS>(cnt, mu, m2, wred);
     mean = mu; ss = m2;
   } else {
+#if TYLO_NORM_F32X2
+    uint64_t q2 = 0ull;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      float f[VEC]; x.p[i].unpack(f);     // packets past the end are zero
+#pragma unroll
+      for (int j = 0; j < VEC; j += 2) {
+        const uint64_t v2 = sm100::pack_f32x2(f[j], f[j + 1]);
+        q2 = sm100::fma_f32x2(v2, v2, q2);
+      }
+    }
+    { float a, b; sm100::unpack_f32x2(q2, a, b); ss = a + b; }
+#else
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       float f[VEC]; x.p[i].unpack(f);     // packets past the end are zero
 #pragma unroll
       for (int j = 0; j < VEC; ++j) ss += f[j] * f[j];
     }
+#endif
     ss = block_reduce<THREADS>(ss, SumOp(), 0.f, red);
   }
   const float rstd = 1.0f / sqrtf(ss * inv_m + eps);
@@ -159,11 +209,31 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
       x.p[i].unpack(f);
       ld_param(W + (size_t)v * VEC).unpack(w);
       if constexpr (LAYER) ld_param(Bias + (size_t)v * VEC).unpack(b);
+#if TYLO_NORM_F32X2
+      if constexpr (LAYER) {
+        // ((x - mean) rstd) w + b on pairs: (x + (-mean)) * (rstd w) + b
+        const uint64_t nmean2 = sm100::pack_f32x2(-mean, -mean), rstd2 = sm100::pack_f32x2(rstd, rstd);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) {
+          const uint64_t c2 = sm100::add_f32x2(sm100::pack_f32x2(f[j], f[j + 1]), nmean2);
+          const uint64_t a2 = sm100::mul_f32x2(sm100::pack_f32x2(w[j], w[j + 1]), rstd2);
+          sm100::unpack_f32x2(sm100::fma_f32x2(c2, a2, sm100::pack_f32x2(b[j], b[j + 1])), f[j], f[j + 1]);
+        }
+      } else {
+        const uint64_t rstd2 = sm100::pack_f32x2(rstd, rstd), off2 = sm100::pack_f32x2(offset, offset);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 2) {
+          const uint64_t a2 = sm100::mul_f32x2(sm100::add_f32x2(sm100::pack_f32x2(w[j], w[j + 1]), off2), rstd2);
+          sm100::unpack_f32x2(sm100::mul_f32x2(sm100::pack_f32x2(f[j], f[j + 1]), a2), f[j], f[j + 1]);
+        }
+      }
+#else
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         if constexpr (LAYER) f[j] = (f[j] - mean) * rstd * w[j] + b[j];
         else f[j] = f[j] * rstd * (w[j] + offset);
       }
+#endif
       x.p[i].pack(f);
     }
   }
@@ -346,15 +416,22 @@ norm_bwd_stream_kernel(T* __restrict__ dX, float* __restrict__ dWp, float* __res
     if constexpr (LAYER) fetch(row + stride, x1, d1, r1, m1);
     else fetch(row + 2 * stride, x2, d2, r2, m2);
     float s1 = 0.f, s2 = 0.f;
+    const uint64_t nm2 = sm100::pack_f32x2(-m0, -m0), r2p = sm100::pack_f32x2(r0, r0);
     {
+      // packed fp32 pairs: xhat = (x - mean) rstd, gd = g dy, s1 += xhat gd, s2 += gd
       float xf[VEC], df[VEC];
       x0.unpack(xf); d0.unpack(df);
+      uint64_t a1 = 0ull, a2 = 0ull;
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        const float gd = g[j] * df[j];
-        s1 += (xf[j] - m0) * r0 * gd;
-        if constexpr (LAYER) s2 += gd;
+      for (int j = 0; j < VEC; j += 2) {
+        const uint64_t gd2 = sm100::mul_f32x2(sm100::pack_f32x2(g[j], g[j + 1]), sm100::pack_f32x2(df[j], df[j + 1]));
+        const uint64_t xh2 = sm100::mul_f32x2(sm100::add_f32x2(sm100::pack_f32x2(xf[j], xf[j + 1]), nm2), r2p);
+        a1 = sm100::fma_f32x2(xh2, gd2, a1);
+        if constexpr (LAYER) a2 = sm100::add_f32x2(a2, gd2);
       }
+      float lo, hi;
+      sm100::unpack_f32x2(a1, lo, hi); s1 = lo + hi;
+      if constexpr (LAYER) { sm100::unpack_f32x2(a2, lo, hi); s2 = lo + hi; }
     }
     s1 = warp_reduce(s1, SumOp());
     if constexpr (LAYER) s2 = warp_reduce(s2, SumOp());
@@ -366,12 +443,22 @@ norm_bwd_stream_kernel(T* __restrict__ dX, float* __restrict__ dWp, float* __res
     // the packets are unpacked again rather than kept as fp32 across the barrier (registers)
     float xf[VEC], df[VEC], o[VEC];
     x0.unpack(xf); d0.unpack(df);
+    const uint64_t nc1 = sm100::pack_f32x2(-c1, -c1), nc2 = sm100::pack_f32x2(-c2, -c2);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      const float xhat = (xf[j] - m0) * r0;
-      o[j] = (g[j] * df[j] - (xhat * c1 + c2)) * r0;     // same formulas as norm_bwd_kernel
-      dw[j] += df[j] * xhat;
-      if constexpr (LAYER) db[j] += df[j];
+    for (int j = 0; j < VEC; j += 2) {
+      // same formulas as norm_bwd_kernel, two columns per instruction:
+      // dx = (g dy - (xhat c1 + c2)) rstd,  dW += dy xhat,  dB += dy
+      const uint64_t df2 = sm100::pack_f32x2(df[j], df[j + 1]);
+      const uint64_t xh2 = sm100::mul_f32x2(sm100::add_f32x2(sm100::pack_f32x2(xf[j], xf[j + 1]), nm2), r2p);
+      const uint64_t t2 = sm100::fma_f32x2(xh2, nc1, nc2);
+      const uint64_t o2 = sm100::mul_f32x2(sm100::fma_f32x2(sm100::pack_f32x2(g[j], g[j + 1]), df2, t2), r2p);
+      sm100::unpack_f32x2(o2, o[j], o[j + 1]);
+      const uint64_t w2 = sm100::fma_f32x2(df2, xh2, sm100::pack_f32x2(dw[j], dw[j + 1]));
+      sm100::unpack_f32x2(w2, dw[j], dw[j + 1]);
+      if constexpr (LAYER) {
+        const uint64_t b2 = sm100::add_f32x2(sm100::pack_f32x2(db[j], db[j + 1]), df2);
+        sm100::unpack_f32x2(b2, db[j], db[j + 1]);
+      }
     }
     Pack<T> out; out.pack(o);
     st_stream(dX + row * M + col, out.raw);
