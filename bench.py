@@ -254,7 +254,7 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
             w["graphed"] = False
         w.update(step=step, work=kv_bytes // world, launches=2, global_work=kv_bytes)
     else:
-        w.update(step=lambda: t.decode_attention_(O, Q, K, V, lengths=lengths, scratch=sc), work=kv_bytes, global_work=kv_bytes)
+        w.update(step=lambda: t.decode_attention_(O, Q, K, V, lengths=lengths, scratch=sc), work=kv_bytes)   # replicas at N > 1
     w["config"] = dict(workload=("split-KV decode, bf16, 1 sequence x 1,048,576 keys" + (f", KV sharded over {world} GPUs, merged by one peer-store exchange launch over NVLink" if world > 1 else ""))
                        if long_ctx else "split-KV decode, bf16, 64 sequences, lengths U[1024,32768]",
                        heads_q=H, heads_kv=Hkv, head_dim=D, n_splits=n_splits, live_kv_bytes=kv_bytes,
