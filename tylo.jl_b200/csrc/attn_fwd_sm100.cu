@@ -112,7 +112,9 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
                                              const uint32_t score_flags, const int X, const int q0x, const int jlo,
                                              const TileRange tr, const int b, const int h, const uint32_t tmem,
                                              const uint32_t sbase, volatile int* abort_flag, T* __restrict__ O,
-                                             float* __restrict__ Mout, float* __restrict__ Lout) {
+                                             float* __restrict__ Mout, float* __restrict__ Lout, const int k_len,
+                                             const int q_lim) {
+  // k_len: keys of this batch entry that exist (<= Sk); q_lim: rows below it are computed and stored
   using SM = FwdSmem<D>;
   auto bar = [&](int i) { return sbase + SM::kBars + 8 * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,7 +137,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
   // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
   // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
   // compare per element against the tile-relative start.
-  int row_lo = 0, row_hi = p.Sk - 1;
+  int row_lo = 0, row_hi = k_len - 1;
   if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) row_hi = min(row_hi, qpos);
   if (mask_flags & TYLO_MASK_SLIDING) row_lo = max(row_lo, qpos - p.window);
   if (mask_flags & TYLO_MASK_PREFIX) row_hi = min(row_hi, p.prefix_len - 1);
@@ -188,7 +190,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
 
     // which tiles need the element-wise mask?
     const int q_lo = q0x + p.input_pos, q_hi = q0x + BM - 1 + p.input_pos;
-    bool partial = kv0 + BN > p.Sk;
+    bool partial = kv0 + BN > k_len;
     if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING | TYLO_MASK_PREFIX_LM)) partial = partial || (kv0 + BN - 1 > q_lo);
     if (mask_flags & TYLO_MASK_SLIDING) partial = partial || (kv0 < q_hi - p.window);
     if (mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM)) partial = true;
@@ -371,7 +373,7 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     inv = l > 0.f ? 1.f / l : 0.f;
   }
   if (ok) {
-    const bool live = row < p.Sq;
+    const bool live = row < q_lim;
     T* og = O + ((size_t)(b * p.H + h) * p.Sq + (live ? row : 0)) * D;
 #pragma unroll
     for (int q = 0; q < D / 32; ++q) {
@@ -426,16 +428,26 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int b = hb / p.H, h = hb % p.H, hk = h / p.G;
   const int q0 = qt * 2 * BM;
 
+  // Ragged batches (attention.jl:25-26,37-46,60): keys at or beyond k_lengths[b] are masked; 64-row
+  // query blocks that start at or beyond q_lengths[b] are skipped and their output rows left untouched.
+  int k_len = p.Sk, q_lim = p.Sq;
+  if (p.k_lengths) { const int v = p.k_lengths[b]; k_len = v < 0 ? 0 : (v > p.Sk ? p.Sk : v); }
+  if (p.q_lengths) {
+    const int v = p.q_lengths[b];
+    const int ql = v < 0 ? 0 : (v > p.Sq ? p.Sq : v);
+    q_lim = min(p.Sq, ((ql + 63) / 64) * 64);
+  }
+
   // key tiles each Q tile can see, as CTA-local index ranges over the union
   int t0[2], t1[2];
 #pragma unroll
   for (int X = 0; X < 2; ++X) {
     const int qx = q0 + X * BM;
     t0[X] = 0; t1[X] = 0;
-    if (qx < p.Sq) {
+    if (qx < q_lim) {
       AttnParams pr = p; pr.mask_flags = mask_flags;
       int lo, hi;
-      kv_range(pr, qx + p.input_pos, min(qx + BM, p.Sq) - 1 + p.input_pos, p.Sk, &lo, &hi);
+      kv_range(pr, qx + p.input_pos, min(qx + BM, p.Sq) - 1 + p.input_pos, k_len, &lo, &hi);
       if (hi > lo) { t0[X] = lo / BN; t1[X] = (hi - 1) / BN + 1; }
     }
   }
@@ -585,7 +597,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int X = (warp >= 8) ? 1 : 0;
     softmax_tile<T, D, MASK, SCORE>(p, mask_flags, score_flags, X, q0 + X * BM, jlo, X ? trB : trA, b, h, tmem, sbase,
-                                    abort_flag, O, Mout, Lout);
+                                    abort_flag, O, Mout, Lout, k_len, q_lim);
   }
 
   tc_fence_before();
@@ -637,7 +649,6 @@ static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int B
 bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype) {
   if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
   if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
-  if (p.k_lengths || p.q_lengths) return false;   // ragged per-batch lengths: generic kernels
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2) return false;
   return true;
 }
