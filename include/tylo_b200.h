@@ -107,6 +107,11 @@ typedef struct {
  * Q (Dk,Sq,H,B)  K (Dk,Sk,Hkv,B)  V (Dv,Sk,Hkv,B)  O (Dv,Sq,H,B);  scale = 1/sqrt(Dk).
  * M, L: optional fp32 (Sq,H,B) checkpoints: M = row max of s*scale*log2(e), L = sum exp2(.-M).
  * k_lengths / q_lengths: optional device int32 (B,) valid lengths (attention.jl:25-26,37-46,60).
+ *   Keys at or beyond k_lengths[b] are masked; 64-row query blocks starting at or beyond
+ *   q_lengths[b] are skipped (forward: their O/M/L rows stay untouched; backward: their gradient
+ *   rows are zero).  As in the reference, masked elements meet probabilities of exactly zero inside
+ *   matrix products, so K, V (and in the backward Q, O, dO) beyond the lengths must hold finite
+ *   values, not uninitialised memory.
  * causal masks kv > q + input_pos.  dtype: storage type of Q,K,V,O.  fp32 storage is computed
  * in true fp32 (the reference's default rounds operands to TF32). */
 int32_t tylo_b200_attention_fwd(void* O, const void* Q, const void* K, const void* V,

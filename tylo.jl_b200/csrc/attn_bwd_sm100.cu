@@ -156,22 +156,24 @@ __device__ __forceinline__ float element(const AttnParams& p, float c, float slo
 // The streamed positions a row of the owned tile can pair with under every mask term except the
 // document comparison: one interval [lo, hi] of row indices of the streamed tensor (queries for a key
 // row in DKDV mode, keys for a query row in DQ mode); mods.jl:101-167 reduced to bounds.
-__device__ __forceinline__ bool row_interval(const AttnParams& p, bool keys_own, int own_row, int* lo_out, int* hi_out) {
+// k_len: keys of this batch entry that exist; q_lim: query rows below it take part (ragged batches).
+__device__ __forceinline__ bool row_interval(const AttnParams& p, bool keys_own, int own_row, int k_len, int q_lim,
+                                             int* lo_out, int* hi_out) {
   const uint32_t m = p.mask_flags;
   int lo = 0, hi;
   bool any;
   if (keys_own) {                      // own row = key kv, streamed = query rows q (position q + input_pos)
     const int kv = own_row;
-    hi = p.Sq - 1;
-    any = kv < p.Sk;
+    hi = q_lim - 1;
+    any = kv < k_len;
     if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) lo = max(lo, kv - p.input_pos);
     if (m & TYLO_MASK_SLIDING) hi = min(hi, kv + p.window - p.input_pos);
     if ((m & TYLO_MASK_PREFIX) && kv >= p.prefix_len) any = false;
     if ((m & TYLO_MASK_PREFIX_LM) && kv >= p.prefix_len) lo = max(lo, kv - p.input_pos);
   } else {                             // own row = query, streamed = keys
     const int qpos = own_row + p.input_pos;
-    hi = p.Sk - 1;
-    any = own_row < p.Sq;
+    hi = k_len - 1;
+    any = own_row < q_lim;
     if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) hi = min(hi, qpos);
     if (m & TYLO_MASK_SLIDING) lo = max(lo, qpos - p.window);
     if (m & TYLO_MASK_PREFIX) hi = min(hi, p.prefix_len - 1);
@@ -203,22 +205,35 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // ---- what this CTA owns and which tiles it streams
   int b, h0, hk, own0;       // own0: first row (key or query) of the owned tile
   int it_lo, it_n, n_iter;   // streamed tile range [it_lo, it_lo + it_n) per head; n_iter over the group
+  // Ragged batches (attention.jl:25-26,60): keys at or beyond k_lengths[b] do not exist; 64-row query
+  // blocks starting at or beyond q_lengths[b] were skipped by the forward and take no part here.
+  int k_len = p.Sk, q_lim = p.Sq;
+  auto batch_lengths = [&](int bb) {
+    if (p.k_lengths) { const int v = p.k_lengths[bb]; k_len = v < 0 ? 0 : (v > p.Sk ? p.Sk : v); }
+    if (p.q_lengths) {
+      const int v = p.q_lengths[bb];
+      const int ql = v < 0 ? 0 : (v > p.Sq ? p.Sq : v);
+      q_lim = min(p.Sq, ((ql + 63) / 64) * 64);
+    }
+  };
   if (MODE == DKDV) {
     const int nkt = (p.Sk + BT - 1) / BT;
     const int nhkb = p.Hkv * p.B;
     const int kt = blockIdx.x / nhkb, hkb = blockIdx.x % nhkb;   // key tile slowest: under a causal mask the
     (void)nkt;                                                    // low tiles carry the most work and start first
     b = hkb / p.Hkv; hk = hkb % p.Hkv; h0 = hk * p.G; own0 = kt * BT;
-    int lo, hi;
-    q_range(p, own0, min(own0 + BT, p.Sk) - 1, p.Sq, &lo, &hi);
+    batch_lengths(b);
+    int lo = 0, hi = 0;
+    if (own0 < k_len) q_range(p, own0, min(own0 + BT, k_len) - 1, q_lim, &lo, &hi);
     it_lo = lo / BT; it_n = hi > lo ? (hi - 1) / BT - it_lo + 1 : 0;
     n_iter = it_n * p.G;
   } else {
     const int nqt = (p.Sq + BT - 1) / BT;
     const int qt = nqt - 1 - (int)(blockIdx.x % nqt), hb = blockIdx.x / nqt;
     b = hb / p.H; h0 = hb % p.H; hk = h0 / p.G; own0 = qt * BT;
-    int lo, hi;
-    kv_range(p, own0 + p.input_pos, min(own0 + BT, p.Sq) - 1 + p.input_pos, p.Sk, &lo, &hi);
+    batch_lengths(b);
+    int lo = 0, hi = 0;
+    if (own0 < q_lim) kv_range(p, own0 + p.input_pos, min(own0 + BT, q_lim) - 1 + p.input_pos, k_len, &lo, &hi);
     it_lo = lo / BT; it_n = hi > lo ? (hi - 1) / BT - it_lo + 1 : 0;
     n_iter = it_n;
   }
@@ -288,7 +303,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const int row = row0 + idx;
           int doc = 0;
           if (MODE == DKDV) {
-            const bool valid = row < p.Sq;
+            const bool valid = row < q_lim;
             const size_t si = (size_t)(b * p.H + h0 + g) * p.Sq + (valid ? row : 0);
             // Both statistics are staged NEGATED, as the addends of the element pass's fused multiply-adds:
             // -lse2, and -Delta (with score mods) or -scale * Delta (without).
@@ -399,7 +414,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     float my_lse = -INFINITY, my_delta = 0.f, slope = 0.f;   // negated, like the staged per-column statistics
     int my_doc = 0;
     if (MODE == DQ) {
-      if (own_row < p.Sq) {
+      if (own_row < q_lim) {
         const size_t si = (size_t)(b * p.H + h0) * p.Sq + own_row;
         my_lse = -lse2g[si]; my_delta = -deltag[si] * (modded ? 1.f : p.scale);
       }
@@ -410,7 +425,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     const bool row_ok = (MODE == DKDV) ? (own_row < p.Sk) : (own_row < p.Sq);
     int iv_lo, iv_hi;
-    const bool iv_any = row_interval(p, MODE == DKDV, own_row, &iv_lo, &iv_hi);
+    const bool iv_any = row_interval(p, MODE == DKDV, own_row, k_len, q_lim, &iv_lo, &iv_hi);
     const unsigned iv_span = iv_any ? (unsigned)(iv_hi - iv_lo) : 0u;
     // soft cap: tanh(x) ~ x (1 - x^2/3 + 2x^4/15 - 17x^6/315) for |x| < 0.4, written in the raw dot product s (x = s k1)
     const float cap_k1 = p.scale * inv_cap, cap_k2 = p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
@@ -428,7 +443,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const int tile0 = (it_lo + ((MODE == DKDV) ? n % it_n : n)) * BT;
       if (MODE == DKDV && (p.score_flags & TYLO_SCORE_ALIBI)) slope = p.slopes[h0 + g];
       const int qa = (MODE == DKDV) ? tile0 : own0, ka = (MODE == DKDV) ? own0 : tile0;
-      bool partial = (ka + BT > p.Sk) || (qa + BT > p.Sq) || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
+      bool partial = (ka + BT > k_len) || (qa + BT > q_lim) || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
       if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) partial = partial || (ka + BT - 1 > qa + p.input_pos);
       if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
 
@@ -793,7 +808,6 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
 bool attn_bwd_sm100_supported(const AttnParams& p, int32_t dtype) {
   if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
   if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
-  if (p.k_lengths || p.q_lengths) return false;   // ragged per-batch lengths: generic kernels
   if (p.d_slopes) return false;                   // score-mod parameter gradients: generic kernels
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2 || (long long)p.Sk * p.Hkv * p.B > 0x7fffffffLL / 2) return false;
   return true;
