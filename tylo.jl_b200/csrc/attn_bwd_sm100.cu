@@ -131,17 +131,20 @@ __device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
 // Returns p; ds0 (already multiplied by the qk scale) through the reference.
 //   nlse, ndelta : the statistics NEGATED (so that they enter as addends of fused multiply-adds)
 //   keep : the pair survives the mask (only read when PARTIAL)     q_minus_kv : position difference (ALiBi)
+//   ds_add : gradient at the additive mods' place in the chain (mods.jl:296-303): times (q - kv) it sums
+//            to the ALiBi slope gradient; a soft cap applied after the additive mod is already in it
 template <bool MODDED, bool PARTIAL>
 __device__ __forceinline__ float element(const AttnParams& p, float c, float slope, float inv_cap, float s, float dp,
-                                         float nlse, float ndelta, int q_minus_kv, bool keep, float& ds0) {
-  float pv, f = p.scale;
+                                         float nlse, float ndelta, int q_minus_kv, bool keep, float& ds0,
+                                         float& ds_add) {
+  float pv, f_inner = p.scale, f_outer = 1.f;
   if (MODDED) {
     float s0 = s * p.scale, sm = s0;
     const bool alibi = p.score_flags & TYLO_SCORE_ALIBI, cap = p.score_flags & TYLO_SCORE_SOFTCAP;
     const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
-    if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
+    if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f_inner *= (1.f - t * t); }
     if (alibi) sm = fmaf(slope, (float)q_minus_kv, sm);
-    if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f *= (1.f - t * t); }
+    if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f_outer = (1.f - t * t); }
     pv = ex2(fmaf(sm, kLog2e, nlse));
   } else {
     pv = ex2(fmaf(s, c, nlse));
@@ -149,7 +152,8 @@ __device__ __forceinline__ float element(const AttnParams& p, float c, float slo
   if (PARTIAL) {
     if (!keep) pv = 0.f;
   }
-  ds0 = pv * (dp + ndelta) * f;
+  ds_add = pv * (dp + ndelta) * f_outer;
+  ds0 = ds_add * f_inner;
   return pv;
 }
 
@@ -426,6 +430,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const bool row_ok = (MODE == DKDV) ? (own_row < p.Sk) : (own_row < p.Sq);
     int iv_lo, iv_hi;
     const bool iv_any = row_interval(p, MODE == DKDV, own_row, k_len, q_lim, &iv_lo, &iv_hi);
+    // ALiBi slope gradient (mods.jl:296-303): the dQ kernel visits every (query, key, head) pair exactly
+    // once, so it accumulates sum ds (q - kv) per thread and adds it to d_slopes[h] once per warp.
+    const bool want_slope_grad = MODE == DQ && p.d_slopes != nullptr && (p.score_flags & TYLO_SCORE_ALIBI);
+    float slope_acc = 0.f;
     const unsigned iv_span = iv_any ? (unsigned)(iv_hi - iv_lo) : 0u;
     // soft cap: tanh(x) ~ x (1 - x^2/3 + 2x^4/15 - 17x^6/315) for |x| < 0.4, written in the raw dot product s (x = s k1)
     const float cap_k1 = p.scale * inv_cap, cap_k2 = p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
@@ -637,8 +645,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                   const int j = q * 32 + t + e;
                   bool keep = (unsigned)(j - rel) <= iv_span;
                   if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
+                  const int qmk = (MODE == DKDV) ? dpos + j : dpos - j;
+                  float ds_add;
                   pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
-                                              lse4[e], del4[e], (MODE == DKDV) ? dpos + j : dpos - j, keep, dd[e]);
+                                              lse4[e], del4[e], qmk, keep, dd[e], ds_add);
+                  if (MODE == DQ && want_slope_grad) slope_acc = fmaf(ds_add, (float)qmk, slope_acc);
                 }
               }
               up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
@@ -661,6 +672,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       mbar_arrive(bar(SM::U2_FULL));
       if (tracer) TYLO_BTRACE(MODE, 1, n, 4);
+    }
+
+    if (want_slope_grad && ok) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) slope_acc += __shfl_xor_sync(0xffffffffu, slope_acc, o);
+      if (lane == 0 && slope_acc != 0.f) atomicAdd(p.d_slopes + h0, slope_acc);
     }
 
     // ---- epilogue: this warpgroup stores columns [wg*D/2, (wg+1)*D/2) of each accumulator
@@ -808,7 +825,6 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
 bool attn_bwd_sm100_supported(const AttnParams& p, int32_t dtype) {
   if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
   if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
-  if (p.d_slopes) return false;                   // score-mod parameter gradients: generic kernels
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2 || (long long)p.Sk * p.Hkv * p.B > 0x7fffffffLL / 2) return false;
   return true;
 }
