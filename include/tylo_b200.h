@@ -155,6 +155,26 @@ int32_t tylo_b200_flex_attention_fwd(void* O, const void* Q, const void* K, cons
                                      int32_t input_pos, float qk_scale, int32_t block_sparse,
                                      int32_t dtype, tylo_stream_t stream);
 
+/* flex_attention!(...; block_mask) → flex_fwd_bm (src/attention/flex.jl:347-360, kernel :107-182):
+ * the forward walks a host-built coarse BlockMask (src/attention/mods.jl:436-476) instead of the
+ * analytic block range.  For query block i (tile_m rows) only the key blocks bm_idx[i][0 .. bm_count[i])
+ * (tile_n keys each, 0-based ids) are visited; where bm_full[i][t] != 0 the mask mod is skipped and
+ * only the key-length bound applies, elsewhere the mask mod is evaluated per pair; pairs in blocks
+ * that are not listed contribute nothing.  bm_count (n_qb), bm_idx and bm_full (n_qb rows of
+ * bm_stride entries — the reference's [n_kb, n_qb] column-major arrays) are device int32.
+ * tile_m and tile_n must be multiples of 32; n_qb = ceil(Sq / tile_m).  There is no backward for
+ * this path (flex.jl:193-194).  Runs on the fp32-arithmetic kernel for every storage type. */
+int32_t tylo_b200_flex_attention_fwd_block_mask(void* O, const void* Q, const void* K, const void* V,
+                                                float* M, float* L,
+                                                const tylo_mask_desc* mask, const tylo_score_desc* score,
+                                                const int32_t* bm_count, const int32_t* bm_idx,
+                                                const int32_t* bm_full, int32_t bm_stride,
+                                                int32_t tile_m, int32_t tile_n,
+                                                int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                                int32_t H, int32_t Hkv, int32_t B,
+                                                int32_t input_pos, float qk_scale,
+                                                int32_t dtype, tylo_stream_t stream);
+
 /* ∇flex_attention! → mha_bwd_preprocess + fill! + flex_bwd (flex.jl:445-511, kernel :197-289;
  * score VJPs mods.jl:288-319). */
 int32_t tylo_b200_flex_attention_bwd(void* dQ, void* dK, void* dV,

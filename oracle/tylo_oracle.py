@@ -149,13 +149,14 @@ def _softmax_cols(S):
 
 def flex_ref(Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec | None = None,
              input_pos: int = 0, qk_scale: float | None = None, doc_per_batch=None,
-             return_stats: bool = False):
+             return_stats: bool = False, keep_dense=None):
     """test/flex.jl:8-35 (flex_ref); with score=None, mask=causal-or-None it is also
     test/attention.jl:9-28 (attn_ref: `n > m` masked == causal with input_pos = 0).
 
     doc_per_batch: optional (B, S) int array — a per-sequence document-id table, the
     extension used for the causal ∧ window ∧ document benchmark config; it overrides
     the mask's 1-D document vector for batch b.
+    keep_dense: optional boolean (Sq, Sk) matrix used instead of `mask` (block-mask path below).
     Returns O (B, H, Sq, Dv) [and natural-base row max M and row sum L, (B, H, Sq)].
     """
     Q = np.asarray(Q, F64); K = np.asarray(K, F64); V = np.asarray(V, F64)
@@ -170,6 +171,9 @@ def flex_ref(Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec | None =
     keep_shared = None
     if mask is not None and doc_per_batch is None:
         keep_shared = mask.dense(q_pos, kv_pos)
+    if keep_dense is not None:
+        keep_shared = np.asarray(keep_dense, dtype=bool)
+        mask = None
     for b in range(B):
         keep = keep_shared
         if mask is not None and doc_per_batch is not None:
@@ -189,6 +193,54 @@ def flex_ref(Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec | None =
     if return_stats:
         return O, Ms, Ls
     return O
+
+
+def build_block_mask_ref(keep, n_q, n_kv, *, TILE_M=64, TILE_N=64, input_pos=0):
+    """src/attention/mods.jl:448-476 (build_block_mask), element by element as the reference does.
+    keep(q, kv) -> bool on 0-based absolute positions.  Returns (count (n_qb,), idx (n_qb, n_kb),
+    full (n_qb, n_kb)) int32 — the reference's [n_kb, n_qb] column-major arrays, same bytes."""
+    nqb, nkb = -(-n_q // TILE_M), -(-n_kv // TILE_N)
+    idx = np.zeros((nqb, nkb), np.int32); full = np.zeros((nqb, nkb), np.int32)
+    cnt = np.zeros(nqb, np.int32)
+    for i in range(nqb):
+        qlo, qhi = i * TILE_M, min((i + 1) * TILE_M, n_q) - 1
+        slot = 0
+        for j in range(nkb):
+            klo, khi = j * TILE_N, min((j + 1) * TILE_N, n_kv) - 1
+            anyk, allk = False, True
+            for q in range(qlo, qhi + 1):
+                for kv in range(klo, khi + 1):
+                    k = bool(keep(q + input_pos, kv))
+                    anyk |= k; allk &= k
+            if anyk:
+                idx[i, slot] = j
+                # boundary blocks are never "full" (mods.jl:468-470)
+                full[i, slot] = 1 if (allk and (i + 1) * TILE_M <= n_q and (j + 1) * TILE_N <= n_kv) else 0
+                slot += 1
+        cnt[i] = slot
+    return cnt, idx, full
+
+
+def flex_block_mask_ref(Q, K, V, count, idx, full, *, TILE_M=64, TILE_N=64, score: ScoreSpec | None = None,
+                        mask: MaskSpec | None = None, input_pos: int = 0, qk_scale: float | None = None,
+                        return_stats: bool = False):
+    """src/attention/flex.jl:107-182 (flex_fwd_bm) on plain arrays: query block i visits only the key
+    blocks idx[i, :count[i]]; in a block marked full the mask mod is skipped (only kv < Sk applies),
+    elsewhere it is evaluated per pair; pairs of unlisted blocks contribute nothing.  The reference has
+    no plain-array version of this walk; its tests compare it with flex_ref under an agreeing mask
+    (test/flex.jl:258-280), which tests/test_oracle_block_mask.py repeats."""
+    Sq, Sk = np.asarray(Q).shape[2], np.asarray(K).shape[2]
+    q_pos = np.arange(Sq) + int(input_pos); kv_pos = np.arange(Sk)
+    dense = mask.dense(q_pos, kv_pos) if mask is not None else np.ones((Sq, Sk), bool)
+    eff = np.zeros((Sq, Sk), bool)
+    for i in range(-(-Sq // TILE_M)):
+        rows = slice(i * TILE_M, min((i + 1) * TILE_M, Sq))
+        for t in range(int(count[i])):
+            j = int(idx[i, t])
+            cols = slice(j * TILE_N, min((j + 1) * TILE_N, Sk))
+            eff[rows, cols] = True if full[i, t] else dense[rows, cols]
+    return flex_ref(Q, K, V, score=score, input_pos=input_pos, qk_scale=qk_scale, return_stats=return_stats,
+                    keep_dense=eff)
 
 
 def attn_ref(Q, K, V, *, causal=False):

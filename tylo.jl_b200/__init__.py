@@ -80,6 +80,8 @@ _SIGS = {
     "tylo_b200_attention_fwd": [_ptr] * 8 + [_i32] * 10 + [_ptr],
     "tylo_b200_attention_bwd": [_ptr] * 13 + [_i64] + [_ptr] * 2 + [_i32] * 10 + [_ptr],
     "tylo_b200_flex_attention_fwd": [_ptr] * 6 + [POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
+    "tylo_b200_flex_attention_fwd_block_mask": [_ptr] * 6 + [POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_ptr] * 3
+                                               + [_i32] * 3 + [_i32] * 8 + [_f32, _i32, _ptr],
     "tylo_b200_flex_attention_bwd": [_ptr] * 13 + [_i64, POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
     "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
@@ -245,6 +247,54 @@ class OrMask(MaskMod):
 
 def prefix_lm(length: int) -> MaskMod:
     return CausalMask() | PrefixMask(length)
+
+
+class BlockMask(NamedTuple):
+    """Precomputed coarse block sparsity (mods.jl:436-440): per query block the key blocks holding any
+    unmasked pair and which of those are fully unmasked.  ``count`` (n_qb,), ``idx`` and ``full``
+    (n_qb, n_kb) are int32 device tensors (the reference's [n_kb, n_qb] column-major arrays); the block
+    edges the mask was built for travel with it.  Forward only (flex.jl:193-194)."""
+    count: torch.Tensor
+    idx: torch.Tensor
+    full: torch.Tensor
+    TILE_M: int = 64
+    TILE_N: int = 64
+
+
+def build_block_mask(keep, n_q: int, n_kv: int, *, TILE_M: int = 64, TILE_N: int = 64, input_pos: int = 0,
+                     device="cuda") -> BlockMask:
+    """build_block_mask(keep, n_q, n_kv; TILE_M, TILE_N, input_pos) (mods.jl:448-476): built on the host
+    from ``keep(q, kv) -> bool`` over 0-based absolute positions, e.g. ``lambda q, kv: hmask(mod, q, kv)``.
+    ``keep`` is first tried on whole index arrays (a predicate written with comparisons works as is)
+    and evaluated pair by pair otherwise.  A block that touches the end of Q or K is never marked full."""
+    import numpy as np
+    nqb, nkb = -(-n_q // TILE_M), -(-n_kv // TILE_N)
+    dense = None
+    try:
+        got = keep(np.arange(n_q, dtype=np.int64)[:, None] + int(input_pos), np.arange(n_kv, dtype=np.int64)[None, :])
+        got = np.asarray(got)
+        if got.shape == (n_q, n_kv) and got.dtype == np.bool_:
+            dense = got
+    except Exception:
+        dense = None
+    if dense is None:
+        dense = np.zeros((n_q, n_kv), dtype=bool)
+        for q in range(n_q):
+            for kv in range(n_kv):
+                dense[q, kv] = bool(keep(q + int(input_pos), kv))
+    idx = np.zeros((nqb, nkb), np.int32); full = np.zeros((nqb, nkb), np.int32); cnt = np.zeros(nqb, np.int32)
+    for i in range(nqb):
+        slot = 0
+        for j in range(nkb):
+            blk = dense[i * TILE_M:(i + 1) * TILE_M, j * TILE_N:(j + 1) * TILE_N]
+            if blk.any():
+                idx[i, slot] = j
+                full[i, slot] = int(blk.all() and (i + 1) * TILE_M <= n_q and (j + 1) * TILE_N <= n_kv)
+                slot += 1
+        cnt[i] = slot
+    dev = torch.device(device)
+    return BlockMask(torch.from_numpy(cnt).to(dev), torch.from_numpy(idx).to(dev), torch.from_numpy(full).to(dev),
+                     int(TILE_M), int(TILE_N))
 
 
 class ScoreMod:
@@ -537,8 +587,6 @@ def _check_bias_shape(sd: _ScoreDesc, Sq: int, Sk: int) -> None:
 def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=None, block_sparse=True,
                     input_pos=0, qk_scale=None, checkpoints=None):
     """flex_attention!(O, Q, K, V; score_mod, mask_mod, ...) (flex.jl:312-383)."""
-    if block_mask is not None:
-        _unsupported("a host-built BlockMask")
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
     _dense(pO, pQ, pK, pV)
@@ -548,6 +596,21 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
     _check_bias_shape(sd, Sq, Sk)
     M = None if checkpoints is None else checkpoints.M
     L = None if checkpoints is None else checkpoints.L
+    if block_mask is not None:
+        # flex.jl:347-360: walk the host-built block list instead of the analytic range
+        bm = block_mask
+        for t in (bm.count, bm.idx, bm.full):
+            if t.dtype != torch.int32:
+                raise TypeError("BlockMask arrays must be int32")
+        _dense(bm.count, bm.idx, bm.full)
+        nqb = -(-Sq // bm.TILE_M)
+        if bm.count.numel() != nqb or bm.idx.dim() != 2 or bm.idx.shape != bm.full.shape or bm.idx.shape[0] != nqb:
+            raise ValueError(f"BlockMask was built for another shape: {nqb} query blocks of {bm.TILE_M} rows expected")
+        _check(_lib.tylo_b200_flex_attention_fwd_block_mask(
+            _p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md), ctypes.byref(sd), _p(bm.count), _p(bm.idx),
+            _p(bm.full), int(bm.idx.shape[1]), int(bm.TILE_M), int(bm.TILE_N), Dk, Dv, Sq, Sk, H, Hkv, B,
+            int(input_pos), 0.0 if qk_scale is None else float(qk_scale), _dtype(pQ), _stream()))
+        return
     _check(_lib.tylo_b200_flex_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md),
                                              ctypes.byref(sd), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
                                              0.0 if qk_scale is None else float(qk_scale), int(bool(block_sparse)),

@@ -192,6 +192,30 @@ extern "C" int32_t tylo_b200_flex_attention_fwd(void* O, const void* Q, const vo
   return attn_fwd_dispatch(O, Q, K, V, M, L, p, dtype, (cudaStream_t)stream);
 }
 
+extern "C" int32_t tylo_b200_flex_attention_fwd_block_mask(
+    void* O, const void* Q, const void* K, const void* V, float* M, float* L, const tylo_mask_desc* mask,
+    const tylo_score_desc* score, const int32_t* bm_count, const int32_t* bm_idx, const int32_t* bm_full,
+    int32_t bm_stride, int32_t tile_m, int32_t tile_n, int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk, int32_t H,
+    int32_t Hkv, int32_t B, int32_t input_pos, float qk_scale, int32_t dtype, tylo_stream_t stream) {
+  const char* who = "flex_attention_fwd_block_mask";
+  TYLO_REQUIRE(O && Q && K && V, TYLO_ERR_INVALID_ARGUMENT, "%s: O, Q, K and V must be non-null", who);
+  TYLO_REQUIRE(bm_count && bm_idx && bm_full, TYLO_ERR_INVALID_ARGUMENT, "%s: count, idx and full must be non-null", who);
+  if (int32_t rc = check_attn_dims(who, Dk, Dv, Sq, Sk, H, Hkv, B)) return rc;
+  TYLO_REQUIRE(tile_m > 0 && tile_n > 0 && tile_m % 32 == 0 && tile_n % 32 == 0, TYLO_ERR_UNSUPPORTED,
+               "%s: block edges must be positive multiples of 32 (TILE_M=%d, TILE_N=%d)", who, tile_m, tile_n);
+  TYLO_REQUIRE(bm_stride > 0, TYLO_ERR_INVALID_ARGUMENT, "%s: bm_stride must be positive", who);
+  TYLO_REQUIRE(aligned16(O) && aligned16(Q) && aligned16(K) && aligned16(V), TYLO_ERR_MISALIGNED,
+               "%s: pointers must be 16-byte aligned", who);
+  AttnParams p;
+  fill_dims(p, Dk, Dv, Sq, Sk, H, Hkv, B, input_pos);
+  if (int32_t rc = fill_mods(who, p, mask, score)) return rc;
+  p.scale = qk_scale > 0.f ? qk_scale : 1.0f / std::sqrt((float)Dk);  // flex.jl:337
+  p.natural_stats = 1; p.block_sparse = 0;
+  p.bm_count = bm_count; p.bm_idx = bm_idx; p.bm_full = bm_full;
+  p.bm_stride = bm_stride; p.bm_tm = tile_m; p.bm_tn = tile_n;
+  return attn_fwd_dispatch(O, Q, K, V, M, L, p, dtype, (cudaStream_t)stream);
+}
+
 extern "C" int32_t tylo_b200_flex_attention_bwd(void* dQ, void* dK, void* dV, const void* Q, const void* K,
                                                 const void* V, const void* O, const void* dO, const float* M,
                                                 const float* L, void* dO_scaled, float* Delta, void* workspace,

@@ -7,7 +7,8 @@
 namespace tylo {
 
 // Score mods that read a (Sk, Sq) table per pair (BiasScore) run on the fp32-arithmetic kernels.
-static bool table_mods(const AttnParams& p) { return (p.score_flags & TYLO_SCORE_BIAS) != 0; }
+// Bias tables and host-built block lists run on the fp32-arithmetic kernels only.
+static bool table_mods(const AttnParams& p) { return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr; }
 
 // TYLO_B200_ATTN_PATH=generic forces the fp32-arithmetic kernels (debugging / A-B checks).
 static bool force_generic() {

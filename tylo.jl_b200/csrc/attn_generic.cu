@@ -108,9 +108,8 @@ attn_fwd_generic_kernel(T* __restrict__ O, const T* __restrict__ Q, const T* __r
 #pragma unroll
   for (int j = 0; j < GMAXJ; ++j) { o[0][j] = 0.f; o[1][j] = 0.f; }
 
-  int lo, hi;
-  kv_range(p, q0 + p.input_pos, min(q0 + GT, p.Sq) - 1 + p.input_pos, k_len, &lo, &hi);
-  for (int kv0 = (lo / GT) * GT; kv0 < hi; kv0 += GT) {
+  // one 32-key tile; use_mask = false skips the mask mod (a block the host marked fully unmasked)
+  auto key_tile = [&](const int kv0, const bool use_mask) {
     __syncthreads();
     load_tile(sK, ldk, Kg, kv0, p.Sk, p.Dk, Dk4);
     load_tile(sV, p.Dv, Vg, kv0, p.Sk, p.Dv, p.Dv);
@@ -124,7 +123,7 @@ attn_fwd_generic_kernel(T* __restrict__ O, const T* __restrict__ Q, const T* __r
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int kv = kv0 + c0 + j;
-        const bool ok = row < p.Sq && kv < k_len && mask_keep(p, b, qpos, kv);
+        const bool ok = row < p.Sq && kv < k_len && (!use_mask || mask_keep(p, b, qpos, kv));
         s[i][j] = ok ? score_apply(p, s[i][j] * p.scale, score_additive(p, slope, b, h, row, qpos, kv)) * kLog2e : -INFINITY;
         mx = fmaxf(mx, s[i][j]);
       }
@@ -159,6 +158,22 @@ attn_fwd_generic_kernel(T* __restrict__ O, const T* __restrict__ Q, const T* __r
         o[0][j] += a0; o[1][j] += a1;
       }
     }
+  };
+  if (p.bm_count) {
+    // walk the host-built block list of this query block (flex.jl:107-182); tile edges are multiples of GT
+    const int qb = q0 / p.bm_tm;
+    const int nb = min(p.bm_count[qb], p.bm_stride);
+    for (int t = 0; t < nb; ++t) {
+      const int j = p.bm_idx[(size_t)qb * p.bm_stride + t];
+      const bool full = p.bm_full[(size_t)qb * p.bm_stride + t] != 0;
+      if (j < 0) continue;
+      const int kend = min((j + 1) * p.bm_tn, p.Sk);
+      for (int kv0 = j * p.bm_tn; kv0 < kend; kv0 += GT) key_tile(kv0, !full);
+    }
+  } else {
+    int lo, hi;
+    kv_range(p, q0 + p.input_pos, min(q0 + GT, p.Sq) - 1 + p.input_pos, k_len, &lo, &hi);
+    for (int kv0 = (lo / GT) * GT; kv0 < hi; kv0 += GT) key_tile(kv0, true);
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {

@@ -28,6 +28,12 @@ struct AttnParams {
   const int32_t* q_lengths;
   int natural_stats;      // 1: M/L in natural units (flex), 0: log2 units (attention!)
   int block_sparse;
+  // Host-built coarse block mask (mods.jl:436-476), forward only: per query block of bm_tm rows the
+  // list of key blocks (bm_tn keys each) to visit and whether mask_mod may be skipped there.
+  const int32_t* bm_count;   // [n_qb]
+  const int32_t* bm_idx;     // [n_qb][bm_stride], 0-based key block ids
+  const int32_t* bm_full;    // [n_qb][bm_stride], != 0: fully unmasked
+  int bm_tm, bm_tn, bm_stride;
 };
 
 // Mask for one (q, kv) pair of absolute 0-based positions (mods.jl:101-167).

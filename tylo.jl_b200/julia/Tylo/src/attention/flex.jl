@@ -7,12 +7,13 @@ export flex_attention!, flex_attention, ∇flex_attention!, ∇flex_attention
 Attention with a score mod applied to the scaled scores and a mask mod (natural-base statistics;
 a fully masked query gives `O = 0`, `M = -Inf`, `L = 0`).  Supported mods: `CausalMask`,
 `SlidingWindowMask`, `DocumentMask`, `PrefixMask`, `prefix_lm` and their `&`; `SoftCapScore`,
-`AliBiScore` and their `∘`.  Anything else, and a host-built `block_mask`, throws `ArgumentError`.
+`AliBiScore`, `BiasScore` and their `∘`; anything else throws `ArgumentError`.  With `block_mask`
+(a `BlockMask` from `build_block_mask`) the forward walks the host-built block list instead of the
+analytic block range; `TILE_M` / `TILE_N` are the edges the mask was built with (multiples of 32).
 """
 function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMask(), block_mask = nothing,
                          block_sparse = true, input_pos = 0, qk_scale = nothing, tensorcore = nothing,
                          TILE_M = 64, TILE_N = 64, checkpoints = nothing)
-    block_mask === nothing || unsupported("a host-built BlockMask")
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     Dk, Dv, Sq, Sk, H, Hkv, B = attn_dims(pQ, pK, pV)
     @assert size(pO) == (Dv, Sq, H, B)
@@ -21,6 +22,21 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
     require_dense(pO, pQ, pK, pV, M, L)
     md = describe!(MaskDesc(), mask_mod)
     sd = describe(score_mod)
+    if block_mask isa BlockMask
+        bm = block_mask
+        @assert length(bm.count) == cld(Sq, TILE_M) && size(bm.idx) == size(bm.full) && size(bm.idx, 2) == length(bm.count)
+        GC.@preserve score_mod mask_mod bm begin
+            check(ccall((:tylo_b200_flex_attention_fwd_block_mask, libtylo), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ref{MaskDesc}, Ref{ScoreDesc},
+                 Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int32, Int32,
+                 Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Float32, Int32, Ptr{Cvoid}),
+                devptr(pO), devptr(pQ), devptr(pK), devptr(pV), devptr(M), devptr(L), md, sd,
+                devptr(bm.count), devptr(bm.idx), devptr(bm.full), Int32(size(bm.idx, 1)), Int32(TILE_M), Int32(TILE_N),
+                Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), qk_scale === nothing ? 0.0f0 : Float32(qk_scale),
+                tylo_dtype(eltype(pQ)), current_stream()))
+        end
+        return
+    end
     GC.@preserve score_mod mask_mod begin
         check(ccall((:tylo_b200_flex_attention_fwd, libtylo), Int32,
             (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ref{MaskDesc}, Ref{ScoreDesc},

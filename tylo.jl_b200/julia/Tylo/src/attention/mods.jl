@@ -3,6 +3,7 @@ export AndMask, OrMask, prefix_lm
 export NoOpScore, SoftCapScore, AliBiScore, BiasScore, ComposeScore
 export hmask, hscore
 export grad_shadow
+export BlockMask, build_block_mask
 
 # Score / mask mods.  The types, constructors and operators are the API; the device side is a set of
 # compiled variants inside libtylo_b200 selected through two plain descriptors.  Calling a mod with
@@ -68,6 +69,46 @@ Base.:|(a::MaskMod, b::MaskMod) = OrMask(a, b)
 
 "Bidirectional over the first `len` positions, causal after."
 prefix_lm(len) = CausalMask() | PrefixMask(Int32(len))
+
+"""
+    BlockMask(count, idx, full)
+
+Host-built coarse block sparsity for `flex_attention!(…; block_mask)`: per query block the 0-based key
+blocks that hold any unmasked pair (`idx[1:count[i], i]`) and whether each is fully unmasked
+(`full`).  Device `Int32` arrays; forward only.
+"""
+struct BlockMask{C,I}
+    count :: C    # [n_qb]
+    idx   :: I    # [n_kb, n_qb]
+    full  :: I    # [n_kb, n_qb]
+end
+
+"""
+    build_block_mask(keep, n_q, n_kv; TILE_M = 64, TILE_N = 64, input_pos = 0, to_device = identity)
+
+Evaluates `keep(q, kv)::Bool` (0-based absolute positions) once per pair on the host and lists, per
+block of `TILE_M` queries, the blocks of `TILE_N` keys with any pair kept; a listed block is marked full
+when every pair is kept and it does not touch the end of Q or K.  `to_device` moves the three `Int32`
+arrays to the GPU (e.g. `CuArray`).
+"""
+function build_block_mask(keep, n_q, n_kv; TILE_M::Int = 64, TILE_N::Int = 64, input_pos::Int = 0, to_device = identity)
+    nqb, nkb = cld(n_q, TILE_M), cld(n_kv, TILE_N)
+    idx, full, cnt = zeros(Int32, nkb, nqb), zeros(Int32, nkb, nqb), zeros(Int32, nqb)
+    for i in 1:nqb
+        qs = (i - 1) * TILE_M : min(i * TILE_M, n_q) - 1
+        slot = 0
+        for j in 1:nkb
+            ks = (j - 1) * TILE_N : min(j * TILE_N, n_kv) - 1
+            kept = count(keep(q + input_pos, kv)::Bool for q in qs, kv in ks)
+            kept == 0 && continue
+            slot += 1
+            idx[slot, i] = j - 1
+            full[slot, i] = (kept == length(qs) * length(ks) && i * TILE_M <= n_q && j * TILE_N <= n_kv) ? 1 : 0
+        end
+        cnt[i] = slot
+    end
+    BlockMask(to_device(cnt), to_device(idx), to_device(full))
+end
 
 struct NoOpScore <: ScoreMod end
 (::NoOpScore)(s, b, h, q, kv) = s
