@@ -67,7 +67,7 @@ int32_t tylo_b200_device_status(int32_t* code);
 #define TYLO_MASK_PREFIX 8u    /* PrefixMask(len): kv < len (mods.jl:127-131) */
 #define TYLO_MASK_PREFIX_LM 16u /* prefix_lm(len) = causal | prefix (mods.jl:178) as one AND term */
 
-typedef struct {
+typedef struct tylo_mask_desc {
   uint32_t flags;
   int32_t window;             /* SLIDING */
   int32_t prefix_len;         /* PREFIX / PREFIX_LM */
@@ -78,6 +78,10 @@ typedef struct {
                                  otherwise element stride between per-batch tables */
   int64_t doc_q_len;          /* number of ids per table (bounds: input_pos + Sq <= doc_q_len) */
   int64_t doc_kv_len;
+  const struct tylo_mask_desc* or_next; /* OrMask (mods.jl:164-167): NULL, or another conjunction OR-ed with this
+                                           one — a mask tree is passed in disjunctive normal form, at most 4
+                                           clauses.  Masks with more than one clause run on the fp32-arithmetic
+                                           kernels without block skipping.  prefix_lm keeps its own flag. */
 } tylo_mask_desc;
 
 #define TYLO_SCORE_ALIBI 1u         /* AliBiScore: s + slopes[h] * (q - kv), one slope per query head (mods.jl:205-209) */
@@ -162,10 +166,29 @@ int32_t tylo_b200_flex_attention_fwd(void* O, const void* Q, const void* K, cons
  * only the key-length bound applies, elsewhere the mask mod is evaluated per pair; pairs in blocks
  * that are not listed contribute nothing.  bm_count (n_qb), bm_idx and bm_full (n_qb rows of
  * bm_stride entries — the reference's [n_kb, n_qb] column-major arrays) are device int32.
- * tile_m and tile_n must be multiples of 32; n_qb = ceil(Sq / tile_m).  There is no backward for
- * this path (flex.jl:193-194).  Runs on the fp32-arithmetic kernel for every storage type. */
+ * tile_m and tile_n must be multiples of 32; n_qb = ceil(Sq / tile_m); the block ids of one query
+ * block must be distinct.  Runs on the fp32-arithmetic kernel for every storage type. */
 int32_t tylo_b200_flex_attention_fwd_block_mask(void* O, const void* Q, const void* K, const void* V,
                                                 float* M, float* L,
+                                                const tylo_mask_desc* mask, const tylo_score_desc* score,
+                                                const int32_t* bm_count, const int32_t* bm_idx,
+                                                const int32_t* bm_full, int32_t bm_stride,
+                                                int32_t tile_m, int32_t tile_n,
+                                                int32_t Dk, int32_t Dv, int32_t Sq, int32_t Sk,
+                                                int32_t H, int32_t Hkv, int32_t B,
+                                                int32_t input_pos, float qk_scale,
+                                                int32_t dtype, tylo_stream_t stream);
+
+/* Backward of the block-list forward above.  The reference has none (flex.jl:193-194: its list is per
+ * query block and its backward loops over key blocks); here every (query tile, key tile) pair looks its
+ * block up in the list, so the gradients are those of exactly the pairs the forward used: listed
+ * blocks only, mask mod skipped where the block is marked full.  Arguments as flex_attention_bwd
+ * (M, L from the block-list forward) plus the list. */
+int32_t tylo_b200_flex_attention_bwd_block_mask(void* dQ, void* dK, void* dV,
+                                                const void* Q, const void* K, const void* V,
+                                                const void* O, const void* dO,
+                                                const float* M, const float* L, float* Delta,
+                                                void* workspace, int64_t workspace_bytes,
                                                 const tylo_mask_desc* mask, const tylo_score_desc* score,
                                                 const int32_t* bm_count, const int32_t* bm_idx,
                                                 const int32_t* bm_full, int32_t bm_stride,

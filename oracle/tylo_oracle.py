@@ -74,6 +74,19 @@ class MaskSpec:
         return keep
 
 
+class MaskAny:
+    """OrMask (mods.jl:164-167): attend where any of the given MaskSpec conjunctions does."""
+
+    def __init__(self, *specs):
+        self.specs = specs
+
+    def dense(self, q_pos: np.ndarray, kv_pos: np.ndarray) -> np.ndarray:
+        keep = np.zeros((q_pos.size, kv_pos.size), dtype=bool)
+        for sp in self.specs:
+            keep |= sp.dense(q_pos, kv_pos)
+        return keep
+
+
 class ScoreSpec:
     """Score mod chain applied to the scaled score s0; mirrors the score mods.
 
@@ -230,6 +243,14 @@ def flex_block_mask_ref(Q, K, V, count, idx, full, *, TILE_M=64, TILE_N=64, scor
     no plain-array version of this walk; its tests compare it with flex_ref under an agreeing mask
     (test/flex.jl:258-280), which tests/test_oracle_block_mask.py repeats."""
     Sq, Sk = np.asarray(Q).shape[2], np.asarray(K).shape[2]
+    eff = block_mask_dense(count, idx, full, Sq, Sk, TILE_M=TILE_M, TILE_N=TILE_N, mask=mask, input_pos=input_pos)
+    return flex_ref(Q, K, V, score=score, input_pos=input_pos, qk_scale=qk_scale, return_stats=return_stats,
+                    keep_dense=eff)
+
+
+def block_mask_dense(count, idx, full, Sq, Sk, *, TILE_M=64, TILE_N=64, mask: MaskSpec | None = None,
+                     input_pos: int = 0):
+    """The pairs the block walk of flex.jl:107-182 lets through, as a boolean (Sq, Sk) matrix."""
     q_pos = np.arange(Sq) + int(input_pos); kv_pos = np.arange(Sk)
     dense = mask.dense(q_pos, kv_pos) if mask is not None else np.ones((Sq, Sk), bool)
     eff = np.zeros((Sq, Sk), bool)
@@ -239,8 +260,16 @@ def flex_block_mask_ref(Q, K, V, count, idx, full, *, TILE_M=64, TILE_N=64, scor
             j = int(idx[i, t])
             cols = slice(j * TILE_N, min((j + 1) * TILE_N, Sk))
             eff[rows, cols] = True if full[i, t] else dense[rows, cols]
-    return flex_ref(Q, K, V, score=score, input_pos=input_pos, qk_scale=qk_scale, return_stats=return_stats,
-                    keep_dense=eff)
+    return eff
+
+
+def flex_block_mask_bwd_ref(dO, Q, K, V, count, idx, full, *, TILE_M=64, TILE_N=64, score: ScoreSpec | None = None,
+                            mask: MaskSpec | None = None, input_pos: int = 0, qk_scale: float | None = None):
+    """Gradients of flex_block_mask_ref: test/flex.jl:75-114 (flex_bwd_ref) over the pairs the block walk
+    lets through.  The reference has no backward for this path (flex.jl:193-194)."""
+    Sq, Sk = np.asarray(Q).shape[2], np.asarray(K).shape[2]
+    eff = block_mask_dense(count, idx, full, Sq, Sk, TILE_M=TILE_M, TILE_N=TILE_N, mask=mask, input_pos=input_pos)
+    return flex_bwd_ref(dO, Q, K, V, score=score, input_pos=input_pos, qk_scale=qk_scale, keep_dense=eff)
 
 
 def attn_ref(Q, K, V, *, causal=False):
@@ -249,7 +278,7 @@ def attn_ref(Q, K, V, *, causal=False):
 
 
 def flex_bwd_ref(dO, Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec | None = None,
-                 input_pos: int = 0, qk_scale: float | None = None, doc_per_batch=None):
+                 input_pos: int = 0, qk_scale: float | None = None, doc_per_batch=None, keep_dense=None):
     """test/flex.jl:75-114 (flex_bwd_ref) == test/attention.jl:30-55 (attn_bwd_ref) when
     there is no score mod.  Returns (dQ, dK, dV, slope_grads) where slope_grads maps the
     index of each ALiBi op in the chain to its (H,) slope gradient (mods.jl:296-303)."""
@@ -271,6 +300,9 @@ def flex_bwd_ref(dO, Q, K, V, *, score: ScoreSpec | None = None, mask: MaskSpec 
     keep_shared = None
     if mask is not None and doc_per_batch is None:
         keep_shared = mask.dense(q_pos, kv_pos)
+    if keep_dense is not None:                  # boolean (Sq, Sk) used instead of `mask` (block-mask path)
+        keep_shared = np.asarray(keep_dense, dtype=bool)
+        mask = None
     for b in range(B):
         keep = keep_shared
         if mask is not None and doc_per_batch is not None:

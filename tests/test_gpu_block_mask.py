@@ -91,3 +91,39 @@ def test_block_edges_must_be_multiples_of_32(tylo):
     bm64 = t.build_block_mask(lambda q, kv: q >= kv, 200, 96)
     with pytest.raises(ValueError):
         t.flex_attention(Q, Q, Q, mask_mod=t.CausalMask(), block_mask=bm64)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("agree", [True, False], ids=["list agrees with mask", "list edited"])
+def test_backward_over_the_listed_blocks(tylo, oracle, dt, agree):
+    """Gradients of the block-list forward (no counterpart in the reference, flex.jl:193-194): the pairs
+    the forward used, and only those, carry gradient."""
+    t, o = tylo, oracle
+    rng = np.random.default_rng(11 + agree)
+    B, H, Hkv, Sq, Sk, D = 2, 4, 2, 200, 260, 64
+    TM, TN = 64, 32
+    Q, Q64 = draw(rng, (B, H, Sq, D), dt); K, K64 = draw(rng, (B, Hkv, Sk, D), dt); V, V64 = draw(rng, (B, Hkv, Sk, D), dt)
+    docs = np.repeat(np.arange(8), 40)[:Sk + 5].astype(np.int32)
+    keep = lambda q, kv: bool(q >= kv and docs[q] == docs[kv])
+    (cnt, idx, full), bm = _bm_from_oracle(t, o, keep, Sq, Sk, TILE_M=TM, TILE_N=TN, input_pos=5)
+    if not agree:
+        cnt = cnt.copy(); full = full.copy()
+        cnt[1] = max(cnt[1] - 1, 0)                 # a listed block dropped: its pairs get no gradient
+        full[2, 0] = 1                              # a partial block marked full: the mask mod is skipped there
+        bm = t.BlockMask(torch.from_numpy(cnt).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(full).cuda(), TM, TN)
+    mask = t.CausalMask() & t.DocumentMask(torch.from_numpy(docs).cuda())
+    omask = o.MaskSpec(causal=True, doc_q=docs)
+    kw = dict(mask_mod=mask, score_mod=t.SoftCapScore(25.0), block_mask=bm, input_pos=5)
+    okw = dict(TILE_M=TM, TILE_N=TN, mask=omask, score=o.ScoreSpec([("softcap", 25.0)]), input_pos=5)
+    cp = t.allocate_checkpoints_flex_attention(Q, K, V)
+    O = t.flex_attention(Q, K, V, checkpoints=cp, **kw)
+    check(O, o.flex_block_mask_ref(Q64, K64, V64, cnt, idx, full, **okw), dt, "block walk fwd")
+    dO, dO64 = draw(rng, tuple(O.shape), dt)
+    dQ, dK, dV = t.grad_flex_attention(dO, Q, K, V, O, checkpoints=cp, **kw)
+    rQ, rK, rV, _ = o.flex_block_mask_bwd_ref(dO64, Q64, K64, V64, cnt, idx, full, **okw)
+    if agree:
+        aQ, aK, aV, _ = o.flex_bwd_ref(dO64, Q64, K64, V64, score=okw["score"], mask=omask, input_pos=5)
+        assert np.allclose(rQ, aQ) and np.allclose(rK, aK) and np.allclose(rV, aV)
+    for got, ref, name in ((dQ, rQ, "dQ"), (dK, rK, "dK"), (dV, rV, "dV")):
+        check(got, ref, dt, f"block walk {name}", scale_hint=float(np.abs(ref).max()) / 4)
+    assert t.device_status() == 0

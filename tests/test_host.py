@@ -31,8 +31,13 @@ def test_mask_descriptor_mapping(tylo):
     assert d.flags == t.MASK_CAUSAL | t.MASK_PREFIX and d.prefix_len == 100
     d = t._mask_desc(None, keep)
     assert d.flags == 0
+    # an OrMask beyond prefix_lm becomes a chain of conjunctions (mods.jl:164-167)
+    d = t._mask_desc(t.PrefixMask(3) | (t.CausalMask() & t.PrefixMask(4)), keep)
+    assert d.flags == t.MASK_PREFIX and d.prefix_len == 3 and d.or_next
+    nxt = t._MaskDesc.from_address(d.or_next)
+    assert nxt.flags == t.MASK_CAUSAL | t.MASK_PREFIX and nxt.prefix_len == 4 and not nxt.or_next
     with pytest.raises(t.TyloError):
-        t._mask_desc(t.PrefixMask(3) | t.PrefixMask(4), keep)
+        t._mask_desc(t.PrefixMask(1) | t.PrefixMask(2) | t.PrefixMask(3) | t.PrefixMask(4) | t.PrefixMask(5), keep)
 
 
 def test_score_descriptor_order(tylo, monkeypatch):

@@ -46,7 +46,7 @@ SCORE_ALIBI, SCORE_SOFTCAP, SCORE_SOFTCAP_FIRST, SCORE_BIAS = 1, 2, 4, 8
 class _MaskDesc(Structure):
     _fields_ = [("flags", c_uint32), ("window", c_int32), ("prefix_len", c_int32), ("reserved", c_int32),
                 ("doc_q", c_void_p), ("doc_kv", c_void_p), ("doc_batch_stride", c_int64),
-                ("doc_q_len", c_int64), ("doc_kv_len", c_int64)]
+                ("doc_q_len", c_int64), ("doc_kv_len", c_int64), ("or_next", c_void_p)]
 
 
 class _ScoreDesc(Structure):
@@ -82,6 +82,8 @@ _SIGS = {
     "tylo_b200_flex_attention_fwd": [_ptr] * 6 + [POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
     "tylo_b200_flex_attention_fwd_block_mask": [_ptr] * 6 + [POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_ptr] * 3
                                                + [_i32] * 3 + [_i32] * 8 + [_f32, _i32, _ptr],
+    "tylo_b200_flex_attention_bwd_block_mask": [_ptr] * 12 + [c_int64, POINTER(_MaskDesc), POINTER(_ScoreDesc)]
+                                               + [_ptr] * 3 + [_i32] * 3 + [_i32] * 8 + [_f32, _i32, _ptr],
     "tylo_b200_flex_attention_bwd": [_ptr] * 13 + [_i64, POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
     "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
@@ -375,40 +377,56 @@ def _unsupported(what):
     raise TyloError(2, f"{what} is not supported by libtylo_b200 (there is no fallback)")
 
 
-def _mask_desc(m: Optional[MaskMod], keep: list) -> Optional[_MaskDesc]:
-    d = _MaskDesc()
+class _PrefixLM(MaskMod):
+    """prefix_lm(len) = CausalMask() | PrefixMask(len) (mods.jl:178) kept as ONE term of a conjunction."""
 
-    def walk(x):
-        if x is None or isinstance(x, FullMask):
-            return
-        if isinstance(x, AndMask):
-            walk(x.a); walk(x.b); return
+    def __init__(self, length: int):
+        self.len = int(length)
+
+    def __call__(self, b, h, q, kv):
+        return q >= kv or kv < self.len
+
+
+_MAX_MASK_CLAUSES = 4
+
+
+def _mask_clauses(x) -> list:
+    """Disjunctive normal form of a mask tree: a list of conjunctions, each a list of atomic masks."""
+    if x is None or isinstance(x, FullMask):
+        return [[]]
+    if isinstance(x, AndMask):
+        return [a + b for a in _mask_clauses(x.a) for b in _mask_clauses(x.b)]
+    if isinstance(x, OrMask):
+        if {type(x.a), type(x.b)} == {CausalMask, PrefixMask}:
+            return [[_PrefixLM(x.a.len if isinstance(x.a, PrefixMask) else x.b.len)]]
+        return _mask_clauses(x.a) + _mask_clauses(x.b)
+    return [[x]]
+
+
+def _clause_desc(terms: list, keep: list) -> _MaskDesc:
+    d = _MaskDesc()
+    for x in terms:
         if isinstance(x, CausalMask):
-            d.flags |= MASK_CAUSAL; return
-        if isinstance(x, SlidingWindowMask):
+            d.flags |= MASK_CAUSAL
+        elif isinstance(x, SlidingWindowMask):
             if d.flags & MASK_SLIDING:
                 d.window = min(d.window, x.w)
             else:
                 d.flags |= MASK_SLIDING; d.window = x.w
-            return
-        if isinstance(x, PrefixMask):
+        elif isinstance(x, PrefixMask):
             if d.flags & MASK_PREFIX:
                 d.prefix_len = min(d.prefix_len, x.len)
             elif d.flags & MASK_PREFIX_LM:
-                _unsupported("PrefixMask combined with prefix_lm")
+                _unsupported("PrefixMask combined with prefix_lm in one conjunction")
             else:
                 d.flags |= MASK_PREFIX; d.prefix_len = x.len
-            return
-        if isinstance(x, OrMask):
-            pair = {type(x.a), type(x.b)}
-            if pair == {CausalMask, PrefixMask} and not d.flags & (MASK_PREFIX | MASK_PREFIX_LM):
-                d.flags |= MASK_PREFIX_LM
-                d.prefix_len = x.a.len if isinstance(x.a, PrefixMask) else x.b.len
-                return
-            _unsupported("OrMask other than prefix_lm")
-        if isinstance(x, DocumentMask):
+        elif isinstance(x, _PrefixLM):
+            if d.flags & (MASK_PREFIX | MASK_PREFIX_LM):
+                _unsupported("prefix_lm combined with another prefix term in one conjunction")
+            d.flags |= MASK_PREFIX_LM; d.prefix_len = x.len
+        elif isinstance(x, DocumentMask):
             if d.flags & MASK_DOCUMENT:
-                _unsupported("more than one DocumentMask")
+                _unsupported("more than one DocumentMask in one conjunction")
             dq, dk = x.doc_q, x.doc_kv
             if dq.dtype != torch.int32 or dk.dtype != torch.int32:
                 raise TypeError("DocumentMask ids must be int32")
@@ -423,11 +441,23 @@ def _mask_desc(m: Optional[MaskMod], keep: list) -> Optional[_MaskDesc]:
                     raise ValueError("per-batch DocumentMask tables must have one shape")
                 d.doc_batch_stride = dq.shape[-1]
             keep.extend([dq, dk])
-            return
-        _unsupported(f"mask mod {type(x).__name__}")
-
-    walk(m)
+        else:
+            _unsupported(f"mask mod {type(x).__name__}")
     return d
+
+
+def _mask_desc(m: Optional[MaskMod], keep: list) -> Optional[_MaskDesc]:
+    """Mask tree -> chain of conjunction descriptors linked through ``or_next`` (AndMask / OrMask,
+    mods.jl:151-167).  One conjunction (the common case) runs on every kernel; several run on the
+    fp32-arithmetic kernels."""
+    clauses = _mask_clauses(m)
+    if len(clauses) > _MAX_MASK_CLAUSES:
+        _unsupported(f"a mask with {len(clauses)} OR-ed conjunctions (at most {_MAX_MASK_CLAUSES})")
+    descs = [_clause_desc(c, keep) for c in clauses]
+    for a, b in zip(descs, descs[1:]):
+        a.or_next = ctypes.addressof(b)
+    keep.extend(descs)
+    return descs[0]
 
 
 def _score_desc(m: Optional[ScoreMod], dm, keep: list) -> _ScoreDesc:
@@ -584,6 +614,16 @@ def _check_bias_shape(sd: _ScoreDesc, Sq: int, Sk: int) -> None:
         raise ValueError(f"BiasScore bias covers {shape} (Sq, Sk) pairs but the call has ({Sq}, {Sk})")
 
 
+def _check_block_mask(bm: BlockMask, Sq: int) -> None:
+    for t in (bm.count, bm.idx, bm.full):
+        if t.dtype != torch.int32:
+            raise TypeError("BlockMask arrays must be int32")
+    _dense(bm.count, bm.idx, bm.full)
+    nqb = -(-Sq // bm.TILE_M)
+    if bm.count.numel() != nqb or bm.idx.dim() != 2 or bm.idx.shape != bm.full.shape or bm.idx.shape[0] != nqb:
+        raise ValueError(f"BlockMask was built for another shape: {nqb} query blocks of {bm.TILE_M} rows expected")
+
+
 def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=None, block_sparse=True,
                     input_pos=0, qk_scale=None, checkpoints=None):
     """flex_attention!(O, Q, K, V; score_mod, mask_mod, ...) (flex.jl:312-383)."""
@@ -599,13 +639,7 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
     if block_mask is not None:
         # flex.jl:347-360: walk the host-built block list instead of the analytic range
         bm = block_mask
-        for t in (bm.count, bm.idx, bm.full):
-            if t.dtype != torch.int32:
-                raise TypeError("BlockMask arrays must be int32")
-        _dense(bm.count, bm.idx, bm.full)
-        nqb = -(-Sq // bm.TILE_M)
-        if bm.count.numel() != nqb or bm.idx.dim() != 2 or bm.idx.shape != bm.full.shape or bm.idx.shape[0] != nqb:
-            raise ValueError(f"BlockMask was built for another shape: {nqb} query blocks of {bm.TILE_M} rows expected")
+        _check_block_mask(bm, Sq)
         _check(_lib.tylo_b200_flex_attention_fwd_block_mask(
             _p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md), ctypes.byref(sd), _p(bm.count), _p(bm.idx),
             _p(bm.full), int(bm.idx.shape[1]), int(bm.TILE_M), int(bm.TILE_N), Dk, Dv, Sq, Sk, H, Hkv, B,
@@ -625,9 +659,11 @@ def flex_attention(Q, K, V, **kw):
 
 
 def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplicated, *, checkpoints,
-                         score_mod=None, mask_mod=None, d_score_mod=None, block_sparse=True, input_pos=0,
-                         qk_scale=None, scratch=None):
-    """∇flex_attention!(...; score_mod, mask_mod, ∂score_mod, checkpoints, scratch) (flex.jl:445-511)."""
+                         score_mod=None, mask_mod=None, d_score_mod=None, block_mask=None, block_sparse=True,
+                         input_pos=0, qk_scale=None, scratch=None):
+    """∇flex_attention!(...; score_mod, mask_mod, ∂score_mod, checkpoints, scratch) (flex.jl:445-511).
+    Extension: ``block_mask`` differentiates the block-list forward (the reference has no backward for it,
+    flex.jl:193-194)."""
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
     if scratch is None:
@@ -639,6 +675,16 @@ def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplica
     sd = _score_desc(score_mod, d_score_mod, keep)
     _check_bias_shape(sd, Sq, Sk)
     ws = scratch.workspace
+    if block_mask is not None:
+        bm = block_mask
+        _check_block_mask(bm, Sq)
+        _check(_lib.tylo_b200_flex_attention_bwd_block_mask(
+            _p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV), _p(pO), _p(dO), _p(checkpoints.M),
+            _p(checkpoints.L), _p(scratch.Delta), _p(ws), 0 if ws is None else ws.numel(), ctypes.byref(md),
+            ctypes.byref(sd), _p(bm.count), _p(bm.idx), _p(bm.full), int(bm.idx.shape[1]), int(bm.TILE_M),
+            int(bm.TILE_N), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos), 0.0 if qk_scale is None else float(qk_scale),
+            _dtype(pQ), _stream()))
+        return
     _check(_lib.tylo_b200_flex_attention_bwd(_p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV),
                                              _p(pO), _p(dO), _p(checkpoints.M), _p(checkpoints.L),
                                              _p(scratch.dO_scaled), _p(scratch.Delta), _p(ws),

@@ -30,23 +30,32 @@ static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* m
   p.mask_flags = 0; p.window = 0; p.prefix_len = 0; p.doc_q = nullptr; p.doc_kv = nullptr; p.doc_stride = 0;
   p.score_flags = 0; p.cap = 1.f; p.slopes = nullptr; p.d_slopes = nullptr;
   p.bias = nullptr; p.d_bias = nullptr; p.bias_heads = 1; p.bias_batch = 1;
-  if (mask) {
+  p.n_or = 0;
+  int n_clauses = 0;
+  for (const tylo_mask_desc* m = mask; m; m = m->or_next, ++n_clauses) {
+    TYLO_REQUIRE(n_clauses <= kMaxOrClauses, TYLO_ERR_UNSUPPORTED, "%s: more than %d OR-ed mask clauses", who,
+                 kMaxOrClauses + 1);
     const uint32_t known = TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING | TYLO_MASK_DOCUMENT | TYLO_MASK_PREFIX |
                            TYLO_MASK_PREFIX_LM;
-    TYLO_REQUIRE((mask->flags & ~known) == 0, TYLO_ERR_UNSUPPORTED, "%s: unknown mask flags 0x%x", who, mask->flags);
-    p.mask_flags = mask->flags; p.window = mask->window; p.prefix_len = mask->prefix_len;
-    if (mask->flags & TYLO_MASK_SLIDING)
-      TYLO_REQUIRE(mask->window >= 0, TYLO_ERR_INVALID_ARGUMENT, "%s: sliding window must be >= 0", who);
-    if (mask->flags & TYLO_MASK_DOCUMENT) {
-      TYLO_REQUIRE(mask->doc_q && mask->doc_kv, TYLO_ERR_INVALID_ARGUMENT,
-                   "%s: DocumentMask needs doc_q and doc_kv", who);
-      TYLO_REQUIRE(mask->doc_q_len >= (int64_t)p.input_pos + p.Sq && p.input_pos >= 0, TYLO_ERR_INVALID_ARGUMENT,
-                   "%s: doc_q holds %lld ids but query positions reach %lld", who, (long long)mask->doc_q_len,
+    TYLO_REQUIRE((m->flags & ~known) == 0, TYLO_ERR_UNSUPPORTED, "%s: unknown mask flags 0x%x", who, m->flags);
+    MaskClause c{m->flags, m->window, m->prefix_len, nullptr, nullptr, 0};
+    if (m->flags & TYLO_MASK_SLIDING)
+      TYLO_REQUIRE(m->window >= 0, TYLO_ERR_INVALID_ARGUMENT, "%s: sliding window must be >= 0", who);
+    if (m->flags & TYLO_MASK_DOCUMENT) {
+      TYLO_REQUIRE(m->doc_q && m->doc_kv, TYLO_ERR_INVALID_ARGUMENT, "%s: DocumentMask needs doc_q and doc_kv", who);
+      TYLO_REQUIRE(m->doc_q_len >= (int64_t)p.input_pos + p.Sq && p.input_pos >= 0, TYLO_ERR_INVALID_ARGUMENT,
+                   "%s: doc_q holds %lld ids but query positions reach %lld", who, (long long)m->doc_q_len,
                    (long long)p.input_pos + p.Sq);
-      TYLO_REQUIRE(mask->doc_kv_len >= p.Sk, TYLO_ERR_INVALID_ARGUMENT,
-                   "%s: doc_kv holds %lld ids but there are %d keys", who, (long long)mask->doc_kv_len, p.Sk);
-      TYLO_REQUIRE(mask->doc_batch_stride >= 0, TYLO_ERR_INVALID_ARGUMENT, "%s: negative doc_batch_stride", who);
-      p.doc_q = mask->doc_q; p.doc_kv = mask->doc_kv; p.doc_stride = mask->doc_batch_stride;
+      TYLO_REQUIRE(m->doc_kv_len >= p.Sk, TYLO_ERR_INVALID_ARGUMENT,
+                   "%s: doc_kv holds %lld ids but there are %d keys", who, (long long)m->doc_kv_len, p.Sk);
+      TYLO_REQUIRE(m->doc_batch_stride >= 0, TYLO_ERR_INVALID_ARGUMENT, "%s: negative doc_batch_stride", who);
+      c.doc_q = m->doc_q; c.doc_kv = m->doc_kv; c.doc_stride = m->doc_batch_stride;
+    }
+    if (n_clauses == 0) {
+      p.mask_flags = c.flags; p.window = c.window; p.prefix_len = c.prefix_len;
+      p.doc_q = c.doc_q; p.doc_kv = c.doc_kv; p.doc_stride = c.doc_stride;
+    } else {
+      p.or_clause[p.n_or++] = c;
     }
   }
   if (score) {
@@ -71,6 +80,19 @@ static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* m
       p.bias = score->bias; p.d_bias = score->d_bias; p.bias_heads = score->bias_heads; p.bias_batch = score->bias_batch;
     }
   }
+  return TYLO_OK;
+}
+
+// Host-built block list (mods.jl:436-476): the analytic block range is not used with it.
+static int32_t fill_block_mask(const char* who, AttnParams& p, const int32_t* count, const int32_t* idx,
+                               const int32_t* full, int32_t stride, int32_t tile_m, int32_t tile_n) {
+  TYLO_REQUIRE(count && idx && full, TYLO_ERR_INVALID_ARGUMENT, "%s: count, idx and full must be non-null", who);
+  TYLO_REQUIRE(tile_m > 0 && tile_n > 0 && tile_m % 32 == 0 && tile_n % 32 == 0, TYLO_ERR_UNSUPPORTED,
+               "%s: block edges must be positive multiples of 32 (TILE_M=%d, TILE_N=%d)", who, tile_m, tile_n);
+  TYLO_REQUIRE(stride > 0, TYLO_ERR_INVALID_ARGUMENT, "%s: bm_stride must be positive", who);
+  p.bm_count = count; p.bm_idx = idx; p.bm_full = full;
+  p.bm_stride = stride; p.bm_tm = tile_m; p.bm_tn = tile_n;
+  p.block_sparse = 0;
   return TYLO_OK;
 }
 
@@ -199,21 +221,34 @@ extern "C" int32_t tylo_b200_flex_attention_fwd_block_mask(
     int32_t Hkv, int32_t B, int32_t input_pos, float qk_scale, int32_t dtype, tylo_stream_t stream) {
   const char* who = "flex_attention_fwd_block_mask";
   TYLO_REQUIRE(O && Q && K && V, TYLO_ERR_INVALID_ARGUMENT, "%s: O, Q, K and V must be non-null", who);
-  TYLO_REQUIRE(bm_count && bm_idx && bm_full, TYLO_ERR_INVALID_ARGUMENT, "%s: count, idx and full must be non-null", who);
   if (int32_t rc = check_attn_dims(who, Dk, Dv, Sq, Sk, H, Hkv, B)) return rc;
-  TYLO_REQUIRE(tile_m > 0 && tile_n > 0 && tile_m % 32 == 0 && tile_n % 32 == 0, TYLO_ERR_UNSUPPORTED,
-               "%s: block edges must be positive multiples of 32 (TILE_M=%d, TILE_N=%d)", who, tile_m, tile_n);
-  TYLO_REQUIRE(bm_stride > 0, TYLO_ERR_INVALID_ARGUMENT, "%s: bm_stride must be positive", who);
   TYLO_REQUIRE(aligned16(O) && aligned16(Q) && aligned16(K) && aligned16(V), TYLO_ERR_MISALIGNED,
                "%s: pointers must be 16-byte aligned", who);
   AttnParams p;
   fill_dims(p, Dk, Dv, Sq, Sk, H, Hkv, B, input_pos);
   if (int32_t rc = fill_mods(who, p, mask, score)) return rc;
+  if (int32_t rc = fill_block_mask(who, p, bm_count, bm_idx, bm_full, bm_stride, tile_m, tile_n)) return rc;
   p.scale = qk_scale > 0.f ? qk_scale : 1.0f / std::sqrt((float)Dk);  // flex.jl:337
-  p.natural_stats = 1; p.block_sparse = 0;
-  p.bm_count = bm_count; p.bm_idx = bm_idx; p.bm_full = bm_full;
-  p.bm_stride = bm_stride; p.bm_tm = tile_m; p.bm_tn = tile_n;
+  p.natural_stats = 1;
   return attn_fwd_dispatch(O, Q, K, V, M, L, p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int32_t tylo_b200_flex_attention_bwd_block_mask(
+    void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+    const float* M, const float* L, float* Delta, void* workspace, int64_t workspace_bytes,
+    const tylo_mask_desc* mask, const tylo_score_desc* score, const int32_t* bm_count, const int32_t* bm_idx,
+    const int32_t* bm_full, int32_t bm_stride, int32_t tile_m, int32_t tile_n, int32_t Dk, int32_t Dv, int32_t Sq,
+    int32_t Sk, int32_t H, int32_t Hkv, int32_t B, int32_t input_pos, float qk_scale, int32_t dtype,
+    tylo_stream_t stream) {
+  const char* who = "flex_attention_bwd_block_mask";
+  if (int32_t rc = check_attn_dims(who, Dk, Dv, Sq, Sk, H, Hkv, B)) return rc;
+  AttnParams p;
+  fill_dims(p, Dk, Dv, Sq, Sk, H, Hkv, B, input_pos);
+  if (int32_t rc = fill_mods(who, p, mask, score)) return rc;
+  if (int32_t rc = fill_block_mask(who, p, bm_count, bm_idx, bm_full, bm_stride, tile_m, tile_n)) return rc;
+  p.scale = qk_scale > 0.f ? qk_scale : 1.0f / std::sqrt((float)Dk);
+  p.natural_stats = 1;
+  return bwd_common(who, dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, workspace, workspace_bytes, p, dtype, stream);
 }
 
 extern "C" int32_t tylo_b200_flex_attention_bwd(void* dQ, void* dK, void* dV, const void* Q, const void* K,

@@ -7,8 +7,10 @@
 namespace tylo {
 
 // Score mods that read a (Sk, Sq) table per pair (BiasScore) run on the fp32-arithmetic kernels.
-// Bias tables and host-built block lists run on the fp32-arithmetic kernels only.
-static bool table_mods(const AttnParams& p) { return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr; }
+// Bias tables, host-built block lists and OR-ed mask clauses run on the fp32-arithmetic kernels only.
+static bool table_mods(const AttnParams& p) {
+  return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr || p.n_or > 0;
+}
 
 // TYLO_B200_ATTN_PATH=generic forces the fp32-arithmetic kernels (debugging / A-B checks).
 static bool force_generic() {

@@ -210,6 +210,17 @@ attn_bwd_delta_kernel(float* __restrict__ Delta, const T* __restrict__ O, const 
   if (lane == 0) Delta[row] = s;
 }
 
+// Host-built block list (mods.jl:436-476) seen from one 32x32 tile: 0 = its (query block, key block) is
+// not listed, 1 = listed, 2 = listed and marked fully unmasked.  Block ids of one query block are distinct.
+__device__ __forceinline__ int bm_state(const AttnParams& p, int q0, int kv0) {
+  const int qb = q0 / p.bm_tm, kb = kv0 / p.bm_tn;
+  const int nb = min(p.bm_count[qb], p.bm_stride);
+  int st = 0;
+  for (int t = 0; t < nb; ++t)
+    if (p.bm_idx[(size_t)qb * p.bm_stride + t] == kb) st = max(st, p.bm_full[(size_t)qb * p.bm_stride + t] != 0 ? 2 : 1);
+  return st;
+}
+
 // Shared by both backward kernels: for the thread's 2x2 patch compute p and the scaled
 // pre-mod score gradient.  Returns the ALiBi slope-gradient contribution of the patch.
 struct BwdPatch { float p[2][2], ds0[2][2]; };
@@ -219,7 +230,7 @@ __device__ __forceinline__ float bwd_patch(const AttnParams& p, int b, int h, fl
                                            const float* sK, const float* sdO, const float* sV, int ldk,
                                            int ldv, int Dk4, int Dv4, int q0, int kv0, int r0, int c0,
                                            int q_lim, int k_len, const float* sLse, const float* sDelta,
-                                           BwdPatch& out) {
+                                           BwdPatch& out, const bool use_mask) {
   float s[2][2], dp[2][2];
   dot2x2(sQ, ldk, sK, ldk, r0, c0, Dk4 / 4, s);
   dot2x2(sdO, ldv, sV, ldv, r0, c0, Dv4 / 4, dp);
@@ -230,7 +241,7 @@ __device__ __forceinline__ float bwd_patch(const AttnParams& p, int b, int h, fl
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int kv = kv0 + c0 + j;
-      const bool ok = row < q_lim && kv < k_len && mask_keep(p, b, qpos, kv);
+      const bool ok = row < q_lim && kv < k_len && (!use_mask || mask_keep(p, b, qpos, kv));
       float pv = 0.f, g0 = 0.f;
       if (ok) {
         const float s0 = s[i][j] * p.scale;
@@ -298,6 +309,8 @@ attn_bwd_dkdv_generic_kernel(T* __restrict__ dK, T* __restrict__ dV, const T* __
     const T* dOg = dO + ((size_t)(b * p.H + h) * p.Sq) * p.Dv;
     const size_t sbase = (size_t)(b * p.H + h) * p.Sq;
     for (int q0 = (qlo / GT) * GT; q0 < qhi; q0 += GT) {
+      const int listed = p.bm_count ? bm_state(p, q0, kv0) : 1;   // uniform over the CTA
+      if (listed == 0) continue;
       __syncthreads();
       load_tile(sQ, ldk, Qg, q0, p.Sq, p.Dk, Dk4);
       load_tile(sdO, ldv, dOg, q0, p.Sq, p.Dv, Dv4);
@@ -308,7 +321,8 @@ attn_bwd_dkdv_generic_kernel(T* __restrict__ dK, T* __restrict__ dV, const T* __
       }
       __syncthreads();
       BwdPatch bp;
-      bwd_patch<false>(p, b, h, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len, sLse, sDelta, bp);
+      bwd_patch<false>(p, b, h, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len, sLse, sDelta, bp,
+                       listed != 2);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -408,13 +422,15 @@ attn_bwd_dq_generic_kernel(T* __restrict__ dQ, const T* __restrict__ Q, const T*
   kv_range(p, q0 + p.input_pos, min(q0 + GT, p.Sq) - 1 + p.input_pos, k_len, &lo, &hi);
   if (q0 >= q_lim) hi = lo;
   for (int kv0 = (lo / GT) * GT; kv0 < hi; kv0 += GT) {
+    const int listed = p.bm_count ? bm_state(p, q0, kv0) : 1;   // uniform over the CTA
+    if (listed == 0) continue;
     __syncthreads();
     load_tile(sK, ldk, Kg, kv0, p.Sk, p.Dk, Dk4);
     load_tile(sV, ldv, Vg, kv0, p.Sk, p.Dv, Dv4);
     __syncthreads();
     BwdPatch bp;
     slope_acc += bwd_patch<true>(p, b, h, slope, sQ, sK, sdO, sV, ldk, ldv, Dk4, Dv4, q0, kv0, r0, c0, q_lim, k_len,
-                           sLse, sDelta, bp);
+                           sLse, sDelta, bp, listed != 2);
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll

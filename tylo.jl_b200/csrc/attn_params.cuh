@@ -8,6 +8,16 @@ namespace tylo {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// One conjunction of mask terms; a mask is clause 0 (the AttnParams fields) OR-ed with `or_clause`s.
+struct MaskClause {
+  uint32_t flags;
+  int window, prefix_len;
+  const int32_t* doc_q;
+  const int32_t* doc_kv;
+  long long doc_stride;
+};
+constexpr int kMaxOrClauses = 3;
+
 struct AttnParams {
   int Dk, Dv, Sq, Sk, H, Hkv, B, G;
   int input_pos;
@@ -34,17 +44,30 @@ struct AttnParams {
   const int32_t* bm_idx;     // [n_qb][bm_stride], 0-based key block ids
   const int32_t* bm_full;    // [n_qb][bm_stride], != 0: fully unmasked
   int bm_tm, bm_tn, bm_stride;
+  // OrMask (mods.jl:164-167) in disjunctive normal form: further clauses OR-ed with the mask above
+  // (fp32-arithmetic kernels only; the analytic block range is not used with them).
+  int n_or;
+  MaskClause or_clause[kMaxOrClauses];
 };
 
 // Mask for one (q, kv) pair of absolute 0-based positions (mods.jl:101-167).
-__device__ __forceinline__ bool mask_keep(const AttnParams& p, int b, int q, int kv) {
+__device__ __forceinline__ bool clause_keep(uint32_t flags, int window, int prefix_len, const int32_t* doc_q,
+                                            const int32_t* doc_kv, long long doc_stride, int b, int q, int kv) {
   bool keep = true;
-  if (p.mask_flags & TYLO_MASK_CAUSAL) keep = keep && (q >= kv);
-  if (p.mask_flags & TYLO_MASK_SLIDING) keep = keep && (q >= kv) && (q <= kv + p.window);
-  if (p.mask_flags & TYLO_MASK_PREFIX) keep = keep && (kv < p.prefix_len);
-  if (p.mask_flags & TYLO_MASK_PREFIX_LM) keep = keep && ((q >= kv) || (kv < p.prefix_len));
-  if (p.mask_flags & TYLO_MASK_DOCUMENT)
-    keep = keep && (p.doc_q[(size_t)b * p.doc_stride + q] == p.doc_kv[(size_t)b * p.doc_stride + kv]);
+  if (flags & TYLO_MASK_CAUSAL) keep = keep && (q >= kv);
+  if (flags & TYLO_MASK_SLIDING) keep = keep && (q >= kv) && (q <= kv + window);
+  if (flags & TYLO_MASK_PREFIX) keep = keep && (kv < prefix_len);
+  if (flags & TYLO_MASK_PREFIX_LM) keep = keep && ((q >= kv) || (kv < prefix_len));
+  if (flags & TYLO_MASK_DOCUMENT)
+    keep = keep && (doc_q[(size_t)b * doc_stride + q] == doc_kv[(size_t)b * doc_stride + kv]);
+  return keep;
+}
+__device__ __forceinline__ bool mask_keep(const AttnParams& p, int b, int q, int kv) {
+  bool keep = clause_keep(p.mask_flags, p.window, p.prefix_len, p.doc_q, p.doc_kv, p.doc_stride, b, q, kv);
+  for (int i = 0; i < p.n_or; ++i) {
+    const MaskClause& c = p.or_clause[i];
+    keep = keep || clause_keep(c.flags, c.window, c.prefix_len, c.doc_q, c.doc_kv, c.doc_stride, b, q, kv);
+  }
   return keep;
 }
 
@@ -96,7 +119,7 @@ __device__ __forceinline__ float score_vjp(const AttnParams& p, float s0, float 
 // (absolute positions): the analytic block lattice of mods.jl:345-413 reduced to the affine masks.
 __device__ __forceinline__ void kv_range(const AttnParams& p, int q_lo, int q_hi, int k_len, int* lo, int* hi) {
   int l = 0, h = k_len;
-  if (p.block_sparse) {
+  if (p.block_sparse && p.n_or == 0) {
     if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) h = min(h, q_hi + 1);
     if (p.mask_flags & TYLO_MASK_SLIDING) l = max(l, q_lo - p.window);
     if (p.mask_flags & TYLO_MASK_PREFIX) h = min(h, p.prefix_len);
@@ -108,7 +131,7 @@ __device__ __forceinline__ void kv_range(const AttnParams& p, int q_lo, int q_hi
 // Query range [lo, hi) (row indices, not positions) that can see keys [kv_lo, kv_hi].
 __device__ __forceinline__ void q_range(const AttnParams& p, int kv_lo, int kv_hi, int q_len, int* lo, int* hi) {
   int l = 0, h = q_len;
-  if (p.block_sparse) {
+  if (p.block_sparse && p.n_or == 0) {
     if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) l = max(l, kv_lo - p.input_pos);
     if (p.mask_flags & TYLO_MASK_SLIDING) h = min(h, kv_hi + p.window - p.input_pos + 1);
   }

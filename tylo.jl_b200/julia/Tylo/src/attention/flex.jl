@@ -20,12 +20,12 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
     M = checkpoints === nothing ? nothing : get(checkpoints, :M, nothing)
     L = checkpoints === nothing ? nothing : get(checkpoints, :L, nothing)
     require_dense(pO, pQ, pK, pV, M, L)
-    md = describe!(MaskDesc(), mask_mod)
+    md, md_chain = describe_mask(mask_mod)
     sd = describe(score_mod)
     if block_mask isa BlockMask
         bm = block_mask
         @assert length(bm.count) == cld(Sq, TILE_M) && size(bm.idx) == size(bm.full) && size(bm.idx, 2) == length(bm.count)
-        GC.@preserve score_mod mask_mod bm begin
+        GC.@preserve score_mod mask_mod md_chain bm begin
             check(ccall((:tylo_b200_flex_attention_fwd_block_mask, libtylo), Int32,
                 (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ref{MaskDesc}, Ref{ScoreDesc},
                  Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int32, Int32,
@@ -37,7 +37,7 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
         end
         return
     end
-    GC.@preserve score_mod mask_mod begin
+    GC.@preserve score_mod mask_mod md_chain begin
         check(ccall((:tylo_b200_flex_attention_fwd, libtylo), Int32,
             (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ref{MaskDesc}, Ref{ScoreDesc},
              Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Float32, Int32, Int32, Ptr{Cvoid}),
@@ -69,8 +69,8 @@ Backward of `flex_attention!` (overwrites the input shadows).  `∂score_mod = g
 accumulates score-mod parameter gradients (ALiBi slopes).
 """
 function ∇flex_attention!(O::Duplicated, Q::Duplicated, K::Duplicated, V::Duplicated; score_mod = NoOpScore(),
-                          mask_mod = FullMask(), ∂score_mod = nothing, block_sparse = true, input_pos = 0,
-                          qk_scale = nothing, tensorcore = nothing, TILE_M = 64, TILE_N = 64, checkpoints,
+                          mask_mod = FullMask(), ∂score_mod = nothing, block_mask = nothing, block_sparse = true,
+                          input_pos = 0, qk_scale = nothing, tensorcore = nothing, TILE_M = 64, TILE_N = 64, checkpoints,
                           scratch = allocate_scratchspace(∇flex_attention!, primal(Q), primal(K), primal(V), primal(O)))
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     Dk, Dv, Sq, Sk, H, Hkv, B = attn_dims(pQ, pK, pV)
@@ -80,9 +80,25 @@ function ∇flex_attention!(O::Duplicated, Q::Duplicated, K::Duplicated, V::Dupl
     ws = get(scratch, :workspace, nothing)
     ws === nothing && (ws = bwd_workspace(pQ, pK, pV))
     require_dense(pO, pQ, pK, pV, shadow(O), shadow(Q), shadow(K), shadow(V), M, L, Δ, ws)
-    md = describe!(MaskDesc(), mask_mod)
+    md, md_chain = describe_mask(mask_mod)
     sd = describe(score_mod, ∂score_mod)
-    GC.@preserve score_mod mask_mod ∂score_mod begin
+    if block_mask isa BlockMask          # gradients of the block-list forward (an extension: upstream has none)
+        bm = block_mask
+        GC.@preserve score_mod mask_mod md_chain ∂score_mod bm begin
+            check(ccall((:tylo_b200_flex_attention_bwd_block_mask, libtylo), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+                 Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Ref{MaskDesc}, Ref{ScoreDesc},
+                 Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int32, Int32,
+                 Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Float32, Int32, Ptr{Cvoid}),
+                devptr(shadow(Q)), devptr(shadow(K)), devptr(shadow(V)), devptr(pQ), devptr(pK), devptr(pV), devptr(pO),
+                devptr(shadow(O)), devptr(M), devptr(L), devptr(Δ), devptr(ws), Int64(length(ws)), md, sd,
+                devptr(bm.count), devptr(bm.idx), devptr(bm.full), Int32(size(bm.idx, 1)), Int32(TILE_M), Int32(TILE_N),
+                Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), qk_scale === nothing ? 0.0f0 : Float32(qk_scale),
+                tylo_dtype(eltype(pQ)), current_stream()))
+        end
+        return
+    end
+    GC.@preserve score_mod mask_mod md_chain ∂score_mod begin
         check(ccall((:tylo_b200_flex_attention_bwd, libtylo), Int32,
             (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
              Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Ref{MaskDesc}, Ref{ScoreDesc},

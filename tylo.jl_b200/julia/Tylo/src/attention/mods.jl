@@ -170,8 +170,9 @@ mutable struct MaskDesc
     doc_batch_stride::Int64
     doc_q_len::Int64
     doc_kv_len::Int64
+    or_next::Ptr{Cvoid}      # next conjunction of the disjunctive normal form, or C_NULL
 end
-MaskDesc() = MaskDesc(0, 0, 0, 0, C_NULL, C_NULL, 0, 0, 0)
+MaskDesc() = MaskDesc(0, 0, 0, 0, C_NULL, C_NULL, 0, 0, 0, C_NULL)
 
 mutable struct ScoreDesc
     flags::UInt32
@@ -214,15 +215,45 @@ function describe!(d::MaskDesc, m::DocumentMask)
     end
     d
 end
-describe!(d::MaskDesc, m::AndMask) = (describe!(d, m.a); describe!(d, m.b))
-function describe!(d::MaskDesc, m::OrMask)
-    a, b = m.a, m.b
-    pm = a isa PrefixMask && b isa CausalMask ? a : (b isa PrefixMask && a isa CausalMask ? b : nothing)
-    (pm === nothing || (d.flags & (MASK_PREFIX | MASK_PREFIX_LM)) != 0) && unsupported("OrMask other than prefix_lm")
-    d.flags |= MASK_PREFIX_LM; d.prefix_len = pm.len
+# prefix_lm(len) = CausalMask() | PrefixMask(len) stays ONE term of a conjunction (its own flag)
+struct PrefixLMTerm <: MaskMod
+    len::Int32
+end
+function describe!(d::MaskDesc, m::PrefixLMTerm)
+    (d.flags & (MASK_PREFIX | MASK_PREFIX_LM)) != 0 && unsupported("prefix_lm combined with another prefix term")
+    d.flags |= MASK_PREFIX_LM; d.prefix_len = m.len
     d
 end
 describe!(::MaskDesc, m::MaskMod) = unsupported("mask mod $(typeof(m))")
+
+# Disjunctive normal form of a mask tree: a vector of conjunctions, each a vector of atomic masks.
+clauses(::FullMask) = [MaskMod[]]
+clauses(m::MaskMod) = [MaskMod[m]]
+clauses(m::AndMask) = [vcat(a, b) for a in clauses(m.a) for b in clauses(m.b)]
+function clauses(m::OrMask)
+    a, b = m.a, m.b
+    a isa PrefixMask && b isa CausalMask && return [MaskMod[PrefixLMTerm(a.len)]]
+    b isa PrefixMask && a isa CausalMask && return [MaskMod[PrefixLMTerm(b.len)]]
+    vcat(clauses(a), clauses(b))
+end
+
+const MAX_MASK_CLAUSES = 4
+
+"""
+    describe_mask(mask_mod) -> (first::MaskDesc, chain::Vector{MaskDesc})
+
+The descriptors of the mask's conjunctions, linked through `or_next`.  `chain` must stay alive
+(`GC.@preserve`) for the duration of the call that receives `first`.
+"""
+function describe_mask(mask_mod::MaskMod)
+    cs = clauses(mask_mod)
+    length(cs) <= MAX_MASK_CLAUSES || unsupported("a mask with $(length(cs)) OR-ed conjunctions")
+    chain = [foldl(describe!, c; init = MaskDesc()) for c in cs]
+    for i in 1:length(chain)-1
+        chain[i].or_next = pointer_from_objref(chain[i+1])
+    end
+    return chain[1], chain
+end
 
 flatten(m::ComposeScore, ∂m) = vcat(flatten(m.a, ∂m === nothing ? nothing : ∂m.a), flatten(m.b, ∂m === nothing ? nothing : ∂m.b))
 flatten(::NoOpScore, ∂m) = Tuple{ScoreMod,Any}[]
