@@ -82,3 +82,37 @@ def test_decode_suggest_splits(tylo):
     assert n >= 64                      # enough CTAs for a 148-SM part with 8 KV heads
     assert tylo.decode_suggest_splits(512, 8, 64) >= 1
     assert tylo.decode_suggest_splits(100, 1, 1) == 1
+
+
+def test_block_mask_and_or_chain_validation(tylo):
+    """Argument checks of the block-list entry points and of OR-ed mask clauses; nothing is launched."""
+    lib = tylo._lib
+    f = _fake
+    md, sd = tylo._MaskDesc(), tylo._ScoreDesc()
+    args_tail = (64, 64, 128, 128, 2, 2, 1, 0, 0.0, 0, None)
+    # block edges that are not multiples of 32 are unsupported
+    rc = lib.tylo_b200_flex_attention_fwd_block_mask(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                                     f(5), f(6), f(7), 2, 48, 64, *args_tail)
+    assert rc == 2 and b"multiples of 32" in lib.tylo_b200_last_error()
+    # the three list arrays are required
+    rc = lib.tylo_b200_flex_attention_fwd_block_mask(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                                     None, f(6), f(7), 2, 64, 64, *args_tail)
+    assert rc == 1 and b"count" in lib.tylo_b200_last_error()
+    # the backward needs the forward's statistics
+    rc = lib.tylo_b200_flex_attention_bwd_block_mask(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), None, None, f(9), None, 0,
+                                                     ctypes.byref(md), ctypes.byref(sd), f(10), f(11), f(12), 2, 64, 64,
+                                                     *args_tail)
+    assert rc == 1 and b"checkpoints" in lib.tylo_b200_last_error()
+    # five OR-ed conjunctions: one more than the library takes
+    chain = [tylo._MaskDesc() for _ in range(5)]
+    for a, b in zip(chain, chain[1:]):
+        a.or_next = ctypes.addressof(b)
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(chain[0]), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
+    assert rc == 2 and b"OR-ed" in lib.tylo_b200_last_error()
+    # a clause further down the chain is validated like the first one
+    chain = [tylo._MaskDesc() for _ in range(2)]
+    chain[0].or_next = ctypes.addressof(chain[1]); chain[1].flags = tylo.MASK_DOCUMENT
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(chain[0]), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
+    assert rc == 1 and b"DocumentMask" in lib.tylo_b200_last_error()
