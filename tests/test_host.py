@@ -61,3 +61,100 @@ def test_duplicated_and_cpu_rejection(tylo):
     assert tylo.primal(d) is x and tylo.shadow(d).shape == x.shape and tylo.primal(x) is x
     with pytest.raises(ValueError):          # device arrays only: there is no CPU path
         tylo.softmax(x)
+
+
+def test_host_tensors_are_refused_before_any_launch(tylo):
+    """A host array must never reach a kernel as an address (the Julia wrapper's `devptr` refuses it the
+    same way): the pointer helper itself raises, as do the block-list and mod descriptors."""
+    t = tylo
+    with pytest.raises(ValueError):
+        t._p(torch.zeros(4))
+    assert t._p(None) is None
+    bm = t.build_block_mask(lambda q, kv: q >= kv, 128, 128, device="cpu")
+    with pytest.raises(ValueError):
+        t._check_block_mask(bm, 128)
+    with pytest.raises(ValueError):
+        t._mask_desc(t.DocumentMask(torch.zeros(8, dtype=torch.int32)), [])
+
+
+class _RbfOp:
+    """Pair op of the kind test/flex.jl:46-60 uses: two radial basis features of a squared distance."""
+
+    def __init__(self, c):
+        self.c = c
+
+    def pair_feature(self, qv, kv):
+        d2 = sum((a - b) ** 2 for a, b in zip(qv, kv))
+        e = torch.exp(-self.c * d2) if isinstance(d2, torch.Tensor) else __import__("math").exp(-self.c * d2)
+        return (e, d2 * e)
+
+    def grad_pair_feature(self, qv, kv, dphi):
+        d2 = sum((a - b) ** 2 for a, b in zip(qv, kv))
+        e = torch.exp(-self.c * d2)
+        g = dphi[0] * (-self.c) * e + dphi[1] * (e - self.c * d2 * e)     # d/d(d2)
+        dq = tuple(g * 2 * (a - b) for a, b in zip(qv, kv))
+        dk = tuple(-x for x in dq)
+        return dq, dk
+
+
+def _pair_mod(t, B=2, Sq=5, Sk=7, F=3, PD=2, H=3, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return t.PairFeatureScore(_RbfOp(0.7), torch.randn(B, Sq, F, generator=g), torch.randn(B, Sk, F, generator=g),
+                              torch.randn(PD, H, generator=g))
+
+
+def test_pair_feature_table_matches_host_evaluation(tylo):
+    """The bias table a PairFeatureScore is lowered to equals its scalar host evaluation (pair.jl:90-96)
+    pair by pair."""
+    t = tylo
+    m = _pair_mod(t)
+    tab = m.bias_table()
+    assert tab.shape == (2, 3, 5, 7)
+    for b in range(2):
+        for h in range(3):
+            for q in range(5):
+                for kv in range(7):
+                    assert float(tab[b, h, q, kv]) == pytest.approx(t.hscore(m, 0.0, q, kv, b=b + 1, h=h + 1), abs=1e-5)
+    low = t._lower_pairs(t.SoftCapScore(5.0) @ m)
+    assert isinstance(low, t.ComposeScore) and isinstance(low.a, t.BiasScore) and isinstance(low.b, t.SoftCapScore)
+
+
+def test_pair_feature_gradients_fold_back(tylo):
+    """Projection and feature gradients recovered from a bias-table gradient equal autograd through the
+    table (pair.jl:127-157 semantics)."""
+    t = tylo
+    m = _pair_mod(t, seed=1)
+    qf, kf, pr = (x.clone().requires_grad_(True) for x in (m.q_features, m.k_features, m.pair_proj))
+    tab = t.PairFeatureScore(m.op, qf, kf, pr).bias_table()
+    d_bias = torch.randn(tab.shape, generator=torch.Generator().manual_seed(2))
+    (tab * d_bias).sum().backward()
+    sh = t.grad_shadow(m, feature_grads=True)
+    m.fold_grads_(sh, d_bias)
+    assert torch.allclose(sh.pair_proj, pr.grad, atol=1e-4)
+    assert torch.allclose(sh.q_features, qf.grad, atol=1e-4) and torch.allclose(sh.k_features, kf.grad, atol=1e-4)
+    sh2 = t.grad_shadow(m)
+    assert sh2.q_features is None and sh2.k_features is None
+    m.fold_grads_(sh2, d_bias)
+    assert torch.allclose(sh2.pair_proj, pr.grad, atol=1e-4)
+
+
+def test_score_tangent_is_generic_over_fields(tylo):
+    """Every array field of a shadow is its own tangent, nested mods recurse, plain fields have none
+    (ext/ChainRulesCoreExt.jl:110-113): a bias table inside a composition keeps its gradient."""
+    t = tylo
+    sh = t.grad_shadow(t.SoftCapScore(5.0) @ t.BiasScore(torch.ones(1, 1, 4, 4)))
+    tan = t.score_tangent(sh)
+    assert set(tan) == {"a", "b"} and tan["a"]["bias"] is sh.a.bias and tan["b"]["cap"] is None
+    tan = t.score_tangent(t.grad_shadow(t.AliBiScore(torch.ones(3))))
+    assert float(tan["slopes"].sum()) == 0.0
+    assert t.score_tangent(t.grad_shadow(_pair_mod(t)))["pair_proj"].shape == (2, 3)
+
+
+def test_adapt_rebuilds_mods(tylo):
+    """adapt(to, mod) maps every array field and keeps the rest (mods.jl:41-44)."""
+    t = tylo
+    docs = torch.arange(6, dtype=torch.int32)
+    m = t.adapt(lambda x: x.to(torch.int64), t.CausalMask() & t.DocumentMask(docs))
+    assert isinstance(m, t.AndMask) and m.b.doc_q.dtype == torch.int64 and t.hmask(m, 3, 3) and not t.hmask(m, 3, 2)
+    s = t.adapt(lambda x: x * 2, t.SoftCapScore(5.0) @ t.AliBiScore(torch.ones(2)))
+    assert s.b.cap == 5.0 and float(s.a.slopes[0]) == 2.0

@@ -134,7 +134,13 @@ def device_status() -> int:
 
 
 def _p(t: Optional[torch.Tensor]):
-    return None if t is None else c_void_p(t.data_ptr())
+    """Raw device address of a tensor (None stays a null pointer).  A host tensor is refused here, before
+    any launch: the kernels would read its address on the GPU (the Julia wrapper's `devptr` does the same)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("libtylo_b200 reads device memory only: got a host tensor; move it to the GPU first")
+    return c_void_p(t.data_ptr())
 
 
 def _stream() -> c_void_p:
@@ -350,6 +356,129 @@ class ComposeScore(ScoreMod):
         return self.b(self.a(s, b, h, q, kv), b, h, q, kv)
 
 
+def pair_feature(op, qvals, kvals):
+    """pair_feature(op, qvals, kvals) -> tuple of PD pair features (pair.jl:37).  User code: ``op`` provides
+    ``pair_feature(qvals, kvals)`` written with broadcasting arithmetic, so that the one definition serves
+    scalars (host evaluation) and (Sq, 1) / (1, Sk) device rows (bias-table construction)."""
+    return op.pair_feature(qvals, kvals)
+
+
+def grad_pair_feature(op, qvals, kvals, dphi):
+    """∇pair_feature(op, qvals, kvals, dphi) -> (dq, dk) (pair.jl:112): the VJP of ``pair_feature``; needed
+    only for feature gradients."""
+    return op.grad_pair_feature(qvals, kvals, dphi)
+
+
+class PairFeatureScore(ScoreMod):
+    """PairFeatureScore(op, q_features, k_features, pair_proj) (pair.jl:49-70):
+    ``s + sum_p pair_proj[h, p] * pair_feature(op, qvals, kvals)[p]`` with ``qvals = q_features[b, q, :]``,
+    ``kvals = k_features[b, kv, :]`` (local positions).  Tensors: q_features (batch, Sq, F), k_features
+    (batch, Sk, F), pair_proj (PD, heads) — Julia's (F, Sq, batch), (F, Sk, batch), (heads, PD).
+
+    The op is user code and cannot be compiled into the library's kernels: the wrappers evaluate it on
+    whole feature rows with device broadcasts into the (batch, heads, Sq, Sk) table of a BiasScore and the
+    kernels run that; gradients of the table are folded back into the projection (and the features)."""
+
+    def __init__(self, op, q_features, k_features, pair_proj):
+        if q_features is not None and k_features is not None and q_features.shape[-1] != k_features.shape[-1]:
+            raise ValueError(f"q_features has {q_features.shape[-1]} feature rows, k_features has {k_features.shape[-1]}")
+        self.op, self.q_features, self.k_features, self.pair_proj = op, q_features, k_features, pair_proj
+
+    def __call__(self, s, b, h, q, kv):
+        F = self.q_features.shape[-1]
+        qv = tuple(float(self.q_features[b - 1, q, f]) for f in range(F))
+        kvv = tuple(float(self.k_features[b - 1, kv, f]) for f in range(F))
+        phi = pair_feature(self.op, qv, kvv)
+        return s + sum(float(self.pair_proj[p, h - 1]) * float(phi[p]) for p in range(self.pair_proj.shape[0]))
+
+    def _rows(self, b):
+        F = self.q_features.shape[-1]
+        return (tuple(self.q_features[b, :, f].float()[:, None] for f in range(F)),
+                tuple(self.k_features[b, :, f].float()[None, :] for f in range(F)))
+
+    def bias_table(self) -> torch.Tensor:
+        """The (batch, heads, Sq, Sk) float32 table this mod stands for."""
+        B, Sq, Sk = self.q_features.shape[0], self.q_features.shape[1], self.k_features.shape[1]
+        PD, H = self.pair_proj.shape
+        out = torch.empty(B, H, Sq, Sk, dtype=torch.float32, device=self.q_features.device)
+        proj = self.pair_proj.float()
+        for b in range(B):
+            phi = pair_feature(self.op, *self._rows(b))
+            stack = torch.stack([torch.broadcast_to(x, (Sq, Sk)) for x in phi])          # (PD, Sq, Sk)
+            out[b] = torch.einsum("ph,pqk->hqk", proj, stack)
+        return out
+
+    def fold_grads_(self, shadow_: "PairFeatureScore", d_bias: torch.Tensor) -> None:
+        """Adds the gradients carried by a bias-table gradient (batch, heads, Sq, Sk) to ``shadow_``."""
+        proj = self.pair_proj.float()
+        for b in range(d_bias.shape[0]):
+            qv, kv = self._rows(b)
+            phi = pair_feature(self.op, qv, kv)
+            Sq, Sk = d_bias.shape[2:]
+            stack = torch.stack([torch.broadcast_to(x, (Sq, Sk)) for x in phi])
+            shadow_.pair_proj += torch.einsum("hqk,pqk->ph", d_bias[b], stack).to(shadow_.pair_proj.dtype)
+            if shadow_.q_features is not None:
+                for h in range(d_bias.shape[1]):
+                    dphi = tuple(proj[p, h] * d_bias[b, h] for p in range(proj.shape[0]))
+                    dq, dk = grad_pair_feature(self.op, qv, kv, dphi)
+                    for f in range(len(qv)):
+                        shadow_.q_features[b, :, f] += torch.broadcast_to(dq[f], (Sq, Sk)).sum(1).to(shadow_.q_features.dtype)
+                        shadow_.k_features[b, :, f] += torch.broadcast_to(dk[f], (Sq, Sk)).sum(0).to(shadow_.k_features.dtype)
+
+
+def _has_pairs(m) -> bool:
+    return isinstance(m, PairFeatureScore) or (isinstance(m, ComposeScore) and (_has_pairs(m.a) or _has_pairs(m.b)))
+
+
+def _lower_pairs(m):
+    """The score chain with every PairFeatureScore replaced by the BiasScore of its table."""
+    if isinstance(m, PairFeatureScore):
+        return BiasScore(m.bias_table())
+    if isinstance(m, ComposeScore):
+        return ComposeScore(_lower_pairs(m.a), _lower_pairs(m.b))
+    return m
+
+
+def _lower_pair_shadows(low, dm):
+    if dm is None:
+        return None
+    if isinstance(dm, PairFeatureScore):
+        return BiasScore(torch.zeros_like(low.bias))
+    if isinstance(dm, ComposeScore):
+        return ComposeScore(_lower_pair_shadows(low.a, dm.a), _lower_pair_shadows(low.b, dm.b))
+    return dm
+
+
+def _raise_pair_grads(dm, m, dlow) -> None:
+    if isinstance(dm, PairFeatureScore):
+        m.fold_grads_(dm, dlow.bias)
+    elif isinstance(dm, ComposeScore):
+        _raise_pair_grads(dm.a, m.a, dlow.a); _raise_pair_grads(dm.b, m.b, dlow.b)
+
+
+def adapt(to, m):
+    """adapt(to, mod): the mod rebuilt with every tensor field passed through ``to`` (mods.jl:41-44), e.g.
+    ``adapt(torch.Tensor.cpu, mod)`` for a host-indexable copy to evaluate with hmask / hscore."""
+    if isinstance(m, torch.Tensor):
+        return to(m)
+    if isinstance(m, (MaskMod, ScoreMod)):
+        out = object.__new__(type(m))
+        for k, v in vars(m).items():
+            setattr(out, k, adapt(to, v))
+        return out
+    return m
+
+
+def score_tangent(dm):
+    """A gradient shadow of a score mod as a plain tangent (ext/ChainRulesCoreExt.jl:110-113): tensors are
+    their own tangent, nested mods become {field: tangent}, anything else has none (None)."""
+    if isinstance(dm, torch.Tensor):
+        return dm
+    if isinstance(dm, ScoreMod):
+        return {k: score_tangent(v) for k, v in vars(dm).items()}
+    return None
+
+
 def hmask(m: MaskMod, q: int, kv: int, *, b: int = 1, h: int = 1) -> bool:
     """Evaluate a mask mod on the host at 0-based positions (mods.jl:53); b, h are 1-based."""
     return bool(m(b, h, q, kv))
@@ -360,8 +489,9 @@ def hscore(m: ScoreMod, s: float, q: int, kv: int, *, b: int = 1, h: int = 1) ->
     return float(m(s, b, h, q, kv))
 
 
-def grad_shadow(x):
-    """Zeroed gradient accumulator for an array or a score mod (mods.jl:281-286)."""
+def grad_shadow(x, *, feature_grads: bool = False):
+    """Zeroed gradient accumulator for an array or a score mod (mods.jl:281-286; pair.jl:121-125 for the
+    opt-in feature gradients of a PairFeatureScore)."""
     if isinstance(x, torch.Tensor):
         return torch.zeros_like(x)
     if isinstance(x, AliBiScore):
@@ -370,6 +500,10 @@ def grad_shadow(x):
         return BiasScore(torch.zeros_like(x.bias))
     if isinstance(x, ComposeScore):
         return ComposeScore(grad_shadow(x.a), grad_shadow(x.b))
+    if isinstance(x, PairFeatureScore):
+        fg = bool(feature_grads)
+        return PairFeatureScore(x.op, torch.zeros_like(x.q_features) if fg else None,
+                                torch.zeros_like(x.k_features) if fg else None, torch.zeros_like(x.pair_proj))
     return x
 
 
@@ -632,6 +766,8 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
     _dense(pO, pQ, pK, pV)
     keep: list = []
     md = _mask_desc(mask_mod, keep)
+    if _has_pairs(score_mod):
+        score_mod = _lower_pairs(score_mod)           # pair features run as bias tables
     sd = _score_desc(score_mod, None, keep)
     _check_bias_shape(sd, Sq, Sk)
     M = None if checkpoints is None else checkpoints.M
@@ -672,6 +808,10 @@ def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplica
     _dense(pO, pQ, pK, pV, dO, Q.shadow, K.shadow, V.shadow)
     keep: list = []
     md = _mask_desc(mask_mod, keep)
+    pair_mod, d_pair_mod = score_mod, d_score_mod
+    if _has_pairs(score_mod):                         # pair features run as bias tables; gradients folded back below
+        score_mod = _lower_pairs(pair_mod)
+        d_score_mod = _lower_pair_shadows(score_mod, d_pair_mod)
     sd = _score_desc(score_mod, d_score_mod, keep)
     _check_bias_shape(sd, Sq, Sk)
     ws = scratch.workspace
@@ -684,6 +824,7 @@ def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplica
             ctypes.byref(sd), _p(bm.count), _p(bm.idx), _p(bm.full), int(bm.idx.shape[1]), int(bm.TILE_M),
             int(bm.TILE_N), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos), 0.0 if qk_scale is None else float(qk_scale),
             _dtype(pQ), _stream()))
+        _raise_pair_grads(d_pair_mod, pair_mod, d_score_mod)
         return
     _check(_lib.tylo_b200_flex_attention_bwd(_p(Q.shadow), _p(K.shadow), _p(V.shadow), _p(pQ), _p(pK), _p(pV),
                                              _p(pO), _p(dO), _p(checkpoints.M), _p(checkpoints.L),
@@ -692,6 +833,7 @@ def grad_flex_attention_(O: Duplicated, Q: Duplicated, K: Duplicated, V: Duplica
                                              Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
                                              0.0 if qk_scale is None else float(qk_scale), int(bool(block_sparse)),
                                              _dtype(pQ), _stream()))
+    _raise_pair_grads(d_pair_mod, pair_mod, d_score_mod)
 
 
 def grad_flex_attention(dO, Q, K, V, O, *, checkpoints, **kw):

@@ -5,7 +5,7 @@ module ChainRulesCoreExt
 # in-place backward — so a captured graph of forward + pullback reuses all memory.
 
 using Tylo
-import Tylo: shadow, _flex_attention, grad_shadow, ScoreMod, AliBiScore, ComposeScore
+import Tylo: shadow, _flex_attention, grad_shadow, ScoreMod
 using ChainRulesCore
 import ChainRulesCore: rrule, unthunk, NoTangent, Tangent
 
@@ -72,10 +72,13 @@ function rrule(::typeof(flex_attention), Q, K, V; kwargs...)
     return O, pullback
 end
 
-# a gradient shadow of a score mod as a ChainRules tangent
-score_tangent(m::AliBiScore, ∂m) = Tangent{typeof(m)}(; slopes = ∂m.slopes)
-score_tangent(m::ComposeScore, ∂m) = Tangent{typeof(m)}(; a = score_tangent(m.a, ∂m.a), b = score_tangent(m.b, ∂m.b))
-score_tangent(m, ∂m) = NoTangent()
+# A gradient shadow (the mod's own struct type, arrays holding gradients, everything else carried along
+# unchanged) as a ChainRules tangent: arrays are their own tangent, nested mods become a `Tangent` over
+# their field names, plain fields (head counts, caps, ops) have none.  Works for every score mod, so a
+# `BiasScore` table or the projection of a `PairFeatureScore` receives its gradient like ALiBi slopes do.
+score_tangent(x::AbstractArray) = x
+score_tangent(m::ScoreMod) = Tangent{typeof(m)}(; (f => score_tangent(getfield(m, f)) for f in fieldnames(typeof(m)))...)
+score_tangent(::Any) = NoTangent()
 
 # gradients with respect to Q, K, V and the score mod's parameters
 function rrule(::typeof(_flex_attention), Q, K, V, score_mod::ScoreMod; mask_mod = Tylo.FullMask(), kwargs...)
@@ -88,7 +91,7 @@ function rrule(::typeof(_flex_attention), Q, K, V, score_mod::ScoreMod; mask_mod
         ∂mod = grad_shadow(score_mod)
         ∇flex_attention!(Duplicated(O, unthunk(Ō)), Qd, Kd, Vd; score_mod, mask_mod, ∂score_mod = ∂mod,
                          checkpoints = cp, scratch = sc, kwargs...)
-        return NoTangent(), shadow(Qd), shadow(Kd), shadow(Vd), score_tangent(score_mod, ∂mod)
+        return NoTangent(), shadow(Qd), shadow(Kd), shadow(Vd), score_tangent(∂mod)
     end
     return O, pullback
 end

@@ -8,10 +8,13 @@
 module Tylo
 
 using CUDACore
+using CUDACore: CuArray
+using Adapt: Adapt, adapt
 
 include("lib.jl")
 include("buffers.jl")
 include("attention/mods.jl")
+include("attention/pair.jl")
 include("attention/flex.jl")
 include("attention/attention.jl")
 include("attention/decode.jl")

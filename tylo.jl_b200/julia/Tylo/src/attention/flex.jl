@@ -7,7 +7,8 @@ export flex_attention!, flex_attention, ∇flex_attention!, ∇flex_attention
 Attention with a score mod applied to the scaled scores and a mask mod (natural-base statistics;
 a fully masked query gives `O = 0`, `M = -Inf`, `L = 0`).  Supported mods: `CausalMask`,
 `SlidingWindowMask`, `DocumentMask`, `PrefixMask`, `prefix_lm` and their `&`; `SoftCapScore`,
-`AliBiScore`, `BiasScore` and their `∘`; anything else throws `ArgumentError`.  With `block_mask`
+`AliBiScore`, `BiasScore`, `PairFeatureScore` (evaluated into a bias table first) and their `∘`; anything
+else throws `ArgumentError`.  With `block_mask`
 (a `BlockMask` from `build_block_mask`) the forward walks the host-built block list instead of the
 analytic block range; `TILE_M` / `TILE_N` are the edges the mask was built with (multiples of 32).
 """
@@ -21,6 +22,7 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
     L = checkpoints === nothing ? nothing : get(checkpoints, :L, nothing)
     require_dense(pO, pQ, pK, pV, M, L)
     md, md_chain = describe_mask(mask_mod)
+    score_mod = has_pairs(score_mod) ? lower_pairs(score_mod) : score_mod     # pair features run as bias tables
     sd = describe(score_mod)
     if block_mask isa BlockMask
         bm = block_mask
@@ -81,6 +83,11 @@ function ∇flex_attention!(O::Duplicated, Q::Duplicated, K::Duplicated, V::Dupl
     ws === nothing && (ws = bwd_workspace(pQ, pK, pV))
     require_dense(pO, pQ, pK, pV, shadow(O), shadow(Q), shadow(K), shadow(V), M, L, Δ, ws)
     md, md_chain = describe_mask(mask_mod)
+    pair_mod, ∂pair_mod = score_mod, ∂score_mod
+    if has_pairs(score_mod)               # pair features run as bias tables; their gradients are folded back below
+        score_mod = lower_pairs(pair_mod)
+        ∂score_mod = lower_pair_shadows(score_mod, ∂pair_mod)
+    end
     sd = describe(score_mod, ∂score_mod)
     if block_mask isa BlockMask          # gradients of the block-list forward (an extension: upstream has none)
         bm = block_mask
@@ -96,6 +103,7 @@ function ∇flex_attention!(O::Duplicated, Q::Duplicated, K::Duplicated, V::Dupl
                 Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), qk_scale === nothing ? 0.0f0 : Float32(qk_scale),
                 tylo_dtype(eltype(pQ)), current_stream()))
         end
+        ∂pair_mod === nothing || raise_pair_grads!(∂pair_mod, pair_mod, ∂score_mod)
         return
     end
     GC.@preserve score_mod mask_mod md_chain ∂score_mod begin
@@ -109,6 +117,7 @@ function ∇flex_attention!(O::Duplicated, Q::Duplicated, K::Duplicated, V::Dupl
             qk_scale === nothing ? 0.0f0 : Float32(qk_scale), Int32(block_sparse), tylo_dtype(eltype(pQ)),
             current_stream()))
     end
+    ∂pair_mod === nothing || raise_pair_grads!(∂pair_mod, pair_mod, ∂score_mod)
     return
 end
 

@@ -13,9 +13,19 @@ export BlockMask, build_block_mask
 abstract type MaskMod end
 abstract type ScoreMod end
 
-"Evaluate a mask mod on the host at scalar positions."
+# `adapt(Array, mod)` gives a host-indexable copy of any mod (and `adapt(CuArray, mod)` the way back):
+# the struct is rebuilt from its adapted fields, field-less mods come back as themselves.  This is how a
+# mod that holds device arrays is evaluated with `hmask` / `hscore` without scalar-indexing the GPU.
+function Adapt.adapt_structure(to, m::Union{MaskMod,ScoreMod})
+    T = typeof(m)
+    n = fieldcount(T)
+    n == 0 && return m
+    return T.name.wrapper((adapt(to, getfield(m, i)) for i in 1:n)...)
+end
+
+"Evaluate a mask mod on the host at scalar positions; for a mod that holds device arrays pass `adapt(Array, mod)`."
 hmask(m::MaskMod, q, kv; b = 1, h = 1) = m(Int32(b), Int32(h), q, kv)
-"Evaluate a score mod on the host for scalar score `s`."
+"Evaluate a score mod on the host for scalar score `s`; for a mod that holds device arrays pass `adapt(Array, mod)`."
 hscore(m::ScoreMod, s, q, kv; b = 1, h = 1) = m(s, Int32(b), Int32(h), q, kv)
 
 "No masking."
@@ -84,14 +94,15 @@ struct BlockMask{C,I}
 end
 
 """
-    build_block_mask(keep, n_q, n_kv; TILE_M = 64, TILE_N = 64, input_pos = 0, to_device = identity)
+    build_block_mask(keep, n_q, n_kv; TILE_M = 64, TILE_N = 64, input_pos = 0, to_device = CuArray)
 
 Evaluates `keep(q, kv)::Bool` (0-based absolute positions) once per pair on the host and lists, per
 block of `TILE_M` queries, the blocks of `TILE_N` keys with any pair kept; a listed block is marked full
-when every pair is kept and it does not touch the end of Q or K.  `to_device` moves the three `Int32`
-arrays to the GPU (e.g. `CuArray`).
+when every pair is kept and it does not touch the end of Q or K.  The three `Int32` arrays are moved to
+the GPU with `to_device` (`CuArray` unless told otherwise), so the result can go straight into
+`flex_attention!(…; block_mask)`; pass `to_device = identity` to keep host arrays for inspection.
 """
-function build_block_mask(keep, n_q, n_kv; TILE_M::Int = 64, TILE_N::Int = 64, input_pos::Int = 0, to_device = identity)
+function build_block_mask(keep, n_q, n_kv; TILE_M::Int = 64, TILE_N::Int = 64, input_pos::Int = 0, to_device = CuArray)
     nqb, nkb = cld(n_q, TILE_M), cld(n_kv, TILE_N)
     idx, full, cnt = zeros(Int32, nkb, nqb), zeros(Int32, nkb, nqb), zeros(Int32, nqb)
     for i in 1:nqb

@@ -10,9 +10,19 @@ tylo_dtype(::Type{Float16}) = Int32(2)
 tylo_dtype(T::Type) = throw(ArgumentError("libtylo_b200 has no kernels for element type $T"))
 
 # ---- the three version-dependent spellings -------------------------------------------------
-"Raw device pointer of a dense device array (`C_NULL` for `nothing`)."
+"""
+    devptr(a)
+
+Raw device address of a dense device array (`C_NULL` for `nothing`).  Only arrays whose `pointer`
+is a device pointer (`CuPtr`) are accepted: a host `Array` here would hand the kernel an address
+the GPU cannot read, so it is refused with an `ArgumentError` before anything is launched.
+"""
 devptr(::Nothing) = Ptr{Cvoid}(C_NULL)
-devptr(a) = reinterpret(Ptr{Cvoid}, UInt(pointer(a)))
+devptr(a::AbstractArray) = devptr(a, pointer(a))
+devptr(a, p::CUDACore.CuPtr) = reinterpret(Ptr{Cvoid}, UInt(p))
+devptr(a, p) = throw(ArgumentError(
+    "libtylo_b200 reads device memory only: got a $(typeof(a)) whose pointer is a $(typeof(p)); move it to the GPU first (e.g. `CuArray(x)`)"))
+devptr(a) = throw(ArgumentError("libtylo_b200 takes device arrays, got a $(typeof(a))"))
 "Handle of the CUDA stream of the current task."
 current_stream() = reinterpret(Ptr{Cvoid}, CUDACore.stream().handle)
 "Whether `a` is a dense column-major array (views with gaps are not accepted)."
