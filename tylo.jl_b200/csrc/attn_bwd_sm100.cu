@@ -35,19 +35,6 @@ using namespace sm100;
 
 __device__ int g_attn_bwd_status = 0;
 
-// Development aid, compiled only with -DTYLO_BWD_TRACE: clock64 stamps of one CTA's hand-offs.
-#ifdef TYLO_BWD_TRACE
-__device__ long long g_bwd_trace[2 * 2 * 64 * 8];
-__device__ int g_bwd_trace_cta = 0;
-#define TYLO_BTRACE(mode, role, it, ev)                                                                    \
-  do {                                                                                                     \
-    if ((int)blockIdx.x == g_bwd_trace_cta && (it) < 64)                                                   \
-      g_bwd_trace[(((mode) * 2 + (role)) * 64 + (it)) * 8 + (ev)] = clock64();                              \
-  } while (0)
-#else
-#define TYLO_BTRACE(mode, role, it, ev) do {} while (0)
-#endif
-
 namespace bwd {
 
 constexpr int BT = 128;            // tile edge (queries and keys)
@@ -397,11 +384,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         ok = mbar_wait(bar(SM::U2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 203);
         if (!ok) break;
-        TYLO_BTRACE(MODE, 0, n, 0);
         tc_fence_after();
         issue_acc2(n);
-        TYLO_BTRACE(MODE, 0, n, 1);
-        if (n + 1 < n_iter) { issue_t2(n + 1); TYLO_BTRACE(MODE, 0, n, 3); }
+        if (n + 1 < n_iter) issue_t2(n + 1);
       }
       tc_commit(bar(SM::DONE));
       mbar_drain(bar(SM::DONE), 0);
@@ -461,8 +446,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
       ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T1_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
       if (!ok) break;
-      const bool tracer = (r == 0 && wg == 0);
-      if (tracer) TYLO_BTRACE(MODE, 1, n, 0);
       tc_fence_after();
       // Document mask: the producer left the smallest and largest id of the streamed tile.  One document
       // that none of this warp's 32 rows belongs to: P = dS = 0 for the warp's rows, nothing to compute.
@@ -497,7 +480,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       uint32_t sv[2][32], dv[2][32];
       tmem_ld32(tmem + lane_off + 64 * wg, sv[0]); tmem_ld32(tmem + lane_off + 64 * wg + 32, sv[1]);
       tc_wait_ld();
-      if (tracer) TYLO_BTRACE(MODE, 1, n, 1);
       const uint32_t stat_u = sbase + SM::kStats + s * SM::kStatStage;   // lse2[128], delta[128], doc[128]
       // column j of this warpgroup's half (streamed row tile0 + 64*wg + j) is inside the row's interval
       // iff (unsigned)(j - rel) <= iv_span; a row that pairs with nothing gets an unreachable start
@@ -551,13 +533,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (MODE == DKDV) tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(SM::U1_FULL));       // T1 columns released: dV's MMAs / the next S may start
-        if (tracer) TYLO_BTRACE(MODE, 1, n, 2);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::T2_FULL), n & 1, abort_flag, &g_attn_bwd_status, 303));
         if (!ok) break;
         tc_fence_after();
         tmem_ld32(tmem + 128 + lane_off + 64 * wg, dv[0]); tmem_ld32(tmem + 128 + lane_off + 64 * wg + 32, dv[1]);
         tc_wait_ld();
-        if (tracer) TYLO_BTRACE(MODE, 1, n, 3);
         // pass 2: ds = p (dp - delta) * scale
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -674,7 +654,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(SM::U2_FULL));
-      if (tracer) TYLO_BTRACE(MODE, 1, n, 4);
     }
 
     if (want_slope_grad && ok) {
@@ -849,14 +828,6 @@ int32_t attn_bwd_sm100(void* dQ, void* dK, void* dV, const void* Q, const void* 
   return bwd::launch<__half, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
 }
 
-#ifdef TYLO_BWD_TRACE
-extern "C" int32_t tylo_b200_debug_bwd_trace(long long* out, int cta) {
-  cudaDeviceSynchronize();
-  if (out) cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * 2 * 2 * 64 * 8);
-  cudaMemcpyToSymbol(g_bwd_trace_cta, &cta, sizeof(int));
-  return 0;
-}
-#endif
 
 int32_t attn_bwd_sm100_status(int* out) {
   int v = 0;

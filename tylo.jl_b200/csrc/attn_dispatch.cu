@@ -1,30 +1,17 @@
 // Chooses, per call, between the tcgen05 kernels and the generic fp32-arithmetic kernels.
 // There is no CPU path: a request no kernel covers returns TYLO_ERR_UNSUPPORTED.
-#include <cstdlib>
-
 #include "attn_dispatch.cuh"
 
 namespace tylo {
 
-// Score mods that read a (Sk, Sq) table per pair (BiasScore) run on the fp32-arithmetic kernels.
 // Bias tables, host-built block lists and OR-ed mask clauses run on the fp32-arithmetic kernels only.
 static bool table_mods(const AttnParams& p) {
   return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr || p.n_or > 0;
 }
 
-// TYLO_B200_ATTN_PATH=generic forces the fp32-arithmetic kernels (debugging / A-B checks).
-static bool force_generic() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("TYLO_B200_ATTN_PATH");
-    v = (e && e[0] == 'g') ? 1 : 0;
-  }
-  return v == 1;
-}
-
 int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                           const AttnParams& p, int32_t dtype, cudaStream_t st) {
-  if (!force_generic() && !table_mods(p) && attn_fwd_sm100_supported(p, dtype)) return attn_fwd_sm100(O, Q, K, V, M, L, p, dtype, st);
+  if (!table_mods(p) && attn_fwd_sm100_supported(p, dtype)) return attn_fwd_sm100(O, Q, K, V, M, L, p, dtype, st);
   TYLO_DISPATCH_DTYPE(dtype, T, return attn_fwd_generic<T>(O, Q, K, V, M, L, p, st));
   return TYLO_OK;
 }
@@ -40,7 +27,7 @@ int64_t attn_bwd_workspace_bytes(int Dk, int Dv, int Sq, int, int H, int, int B,
 int32_t attn_bwd_dispatch(void* dQ, void* dK, void* dV, const void* Q, const void* K, const void* V,
                           const void* O, const void* dO, const float* M, const float* L, float* Delta,
                           void* workspace, const AttnParams& p, int32_t dtype, cudaStream_t st) {
-  if (!force_generic() && !table_mods(p) && attn_bwd_sm100_supported(p, dtype))
+  if (!table_mods(p) && attn_bwd_sm100_supported(p, dtype))
     return attn_bwd_sm100(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, workspace, p, dtype, st);
   TYLO_DISPATCH_DTYPE(dtype, T, return attn_bwd_generic<T>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, p, st));
   return TYLO_OK;

@@ -32,18 +32,6 @@ using namespace sm100;
 
 __device__ int g_attn_fwd_status = 0;
 
-// Development aid, compiled only with -DTYLO_FWD_TRACE: clock64 stamps of one CTA's hand-offs.
-#ifdef TYLO_FWD_TRACE
-__device__ long long g_fwd_trace[3 * 64 * 8];
-__device__ int g_fwd_trace_cta = 0;
-#define TYLO_TRACE(role, tile, ev)                                                              \
-  do {                                                                                          \
-    if ((int)blockIdx.x == g_fwd_trace_cta && (tile) < 64) g_fwd_trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define TYLO_TRACE(role, tile, ev) do {} while (0)
-#endif
-
 constexpr uint32_t kRuntimeMods = 0x80000000u;  // template value: read the flags from AttnParams
 constexpr int BM = 128, BN = 128;               // rows of one Q tile, keys of one K/V tile
 constexpr int kFwdThreads = 384;
@@ -83,9 +71,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-#ifndef TYLO_FWD_F32X2
-#define TYLO_FWD_F32X2 1   // 0: scalar fp32 in the element loops (A/B aid)
-#endif
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -164,8 +149,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     }
     ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::S_FULL + X), i & 1, abort_flag, &g_attn_fwd_status, 301));
     if (!ok) break;
-    const bool tracer = (r == 0);
-    if (tracer) TYLO_TRACE(1 + X, i, 0);
     tc_fence_after();
     // P = 0 for the whole tile: nothing to load, exponentiate or rescale
     auto pass_empty_tile = [&]() {
@@ -186,7 +169,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
 #pragma unroll
     for (int q = 0; q < 4; ++q) tmem_ld32(ts + q * 32, sr[q]);
     tc_wait_ld();
-    if (tracer) TYLO_TRACE(1 + X, i, 1);
 
     // which tiles need the element-wise mask?
     const int q_lo = q0x + p.input_pos, q_hi = q0x + BM - 1 + p.input_pos;
@@ -213,7 +195,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       }
       if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * cap_k1 < 0.4f)) {
         // cap*log2e*tanh(x), x = s*k1:  x (1 - x^2/3 + 2x^4/15 - 17x^6/315) = s * (a0 + u (a1 + u (a2 + u a3))), u = s^2
-#if TYLO_FWD_F32X2
         const uint64_t a0 = pack_f32x2(cap_a0, cap_a0), a1 = pack_f32x2(cap_a1, cap_a1), a2 = pack_f32x2(cap_a2, cap_a2),
                        a3 = pack_f32x2(cap_a3, cap_a3);
 #pragma unroll
@@ -227,16 +208,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
             sr[q][t] = __float_as_uint(y0); sr[q][t + 1] = __float_as_uint(y1);
           }
         }
-#else
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            const float s = __uint_as_float(sr[q][t]), u = s * s;
-            sr[q][t] = __float_as_uint(s * fmaf(u, fmaf(u, fmaf(u, cap_a3, cap_a2), cap_a1), cap_a0));
-          }
-        }
-#endif
         mods_done = true;
       }
     }
@@ -255,7 +226,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
         }
       }
     }
-    if (tracer) TYLO_TRACE(1 + X, i, 6);
     if (partial) {
       // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
       // runtime condition makes the compiler wrap every one of the 128 in a convergence barrier.
@@ -279,7 +249,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       };
       if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
     }
-    if (tracer) TYLO_TRACE(1 + X, i, 7);
     float mxq[4][2];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -293,7 +262,6 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     const float mx = fmaxf(fmaxf(max3(mxq[0][0], mxq[0][1], mxq[1][0]), max3(mxq[1][1], mxq[2][0], mxq[2][1])),
                            fmaxf(mxq[3][0], mxq[3][1]));
     m_true = fmaxf(m_true, mx);
-    if (tracer) TYLO_TRACE(1 + X, i, 2);
     if (__all_sync(0xffffffffu, mx == -INFINITY)) {
       // every pair of this warp's 32 rows is masked in this tile (e.g. keys of another document):
       pass_empty_tile();
@@ -321,35 +289,24 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       }
       if (need) m_ref = mx;
     }
-    if (tracer) TYLO_TRACE(1 + X, i, 3);
     const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
     float lsq[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-#if TYLO_FWD_F32X2
     // Two scores per instruction on the FMA pipe: fma.rn.f32x2 for the exponent arguments and
     // add.rn.f32x2 for the running row sums (register pairs, sm_100 packed fp32).
     const uint64_t c2 = pack_f32x2(c, c), mc2 = pack_f32x2(-mc, -mc);
     uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
-#endif
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t pk[16];
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-#if TYLO_FWD_F32X2
         float x0, x1;
         unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[q][2 * t]), __uint_as_float(sr[q][2 * t + 1])), c2, mc2), x0, x1);
         const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
         ls2[q] = add_f32x2(ls2[q], pack_f32x2(p0, p1));
-#else
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q][2 * t]), c, -mc));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q][2 * t + 1]), c, -mc));
-        lsq[q][0] += p0; lsq[q][1] += p1;
-#endif
         pk[t] = pack_pair<T>(p0, p1);
       }
-#if TYLO_FWD_F32X2
       unpack_f32x2(ls2[q], lsq[q][0], lsq[q][1]);
-#endif
       // 16 columns of packed pairs = 32 probabilities
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -358,11 +315,9 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
             "r"(pk[15]) : "memory");
     }
     l += ((lsq[0][0] + lsq[0][1]) + (lsq[1][0] + lsq[1][1])) + ((lsq[2][0] + lsq[2][1]) + (lsq[3][0] + lsq[3][1]));
-    if (tracer) TYLO_TRACE(1 + X, i, 4);
     tc_wait_st();
     tc_fence_before();
     mbar_arrive(bar(SM::P_FULL + X));
-    if (tracer) TYLO_TRACE(1 + X, i, 5);
   }
 
   // ---- epilogue: O / l, M, L   (tcgen05.ld is warp-collective: every lane loads, stores are predicated)
@@ -570,10 +525,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               const TileRange& t = X ? trB : trA;
               ok = ok && mbar_wait(bar(SM::P_FULL + X), (j - t.s) & 1, abort_flag, &g_attn_fwd_status, 205);
               if (!ok) break;
-              TYLO_TRACE(0, j, X * 4 + 0);
               tc_fence_after();
               issue_pv(X, j);
-              TYLO_TRACE(0, j, X * 4 + 1);
             }
             if (j + 1 < n_tot && active(X, j + 1)) {
               if (!k_ready) {
@@ -581,10 +534,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 k_ready = true;
               }
               if (!ok) break;
-              TYLO_TRACE(0, j, X * 4 + 2);
               tc_fence_after();
               issue_qk(X, j + 1);
-              TYLO_TRACE(0, j, X * 4 + 3);
             }
           }
           if (!ok) break;
@@ -698,14 +649,6 @@ int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, flo
   return dispatch_mods<__half, 64>(mq, mk, mv, O, M, L, p, st);
 }
 
-#ifdef TYLO_FWD_TRACE
-extern "C" int32_t tylo_b200_debug_fwd_trace(long long* out, int cta) {
-  cudaDeviceSynchronize();
-  if (out) cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(long long) * 3 * 64 * 8);
-  cudaMemcpyToSymbol(g_fwd_trace_cta, &cta, sizeof(int));
-  return 0;
-}
-#endif
 
 int32_t attn_fwd_sm100_status(int* out) {
   int v = 0;

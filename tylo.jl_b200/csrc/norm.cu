@@ -13,9 +13,6 @@
 #include "rowwise.cuh"
 #include "sm100_ptx.cuh"
 
-#ifndef TYLO_NORM_F32X2
-#define TYLO_NORM_F32X2 1   // 0: scalar fp32 in the forward element loops (A/B aid)
-#endif
 
 namespace tylo {
 
@@ -121,7 +118,6 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
     // Per-thread mean and centred second moment from the registers, then ONE reduction round that
     // merges (count, mean, M2) triples (Chan et al.): centred accuracy without a second barrier.
     float cnt = 0.f, s = 0.f;
-#if TYLO_NORM_F32X2
     // two elements per instruction (packed fp32 pairs): the kernel is close enough to the issue limit
     // for the instruction count to show in its bandwidth
     uint64_t s2 = 0ull;
@@ -150,31 +146,10 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
       }
     }
     { float a, b; sm100::unpack_f32x2(q2, a, b); m2 = a + b; }
-#else
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      if (i * THREADS + (int)threadIdx.x < nvec) {
-        float f[VEC]; x.p[i].unpack(f);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) s += f[j];
-        cnt += (float)VEC;
-      }
-    }
-    float mu = cnt > 0.f ? s / cnt : 0.f, m2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      if (i * THREADS + (int)threadIdx.x < nvec) {
-        float f[VEC]; x.p[i].unpack(f);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) { const float c = f[j] - mu; m2 += c * c; }
-      }
-    }
-#endif
     if (nvec == THREADS * ITERS) welford_block_equal<THREADS>((float)(ITERS * VEC), mu, m2, wred);
     else welford_block<THREADS>(cnt, mu, m2, wred);
     mean = mu; ss = m2;
   } else {
-#if TYLO_NORM_F32X2
     uint64_t q2 = 0ull;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
@@ -186,14 +161,6 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
       }
     }
     { float a, b; sm100::unpack_f32x2(q2, a, b); ss = a + b; }
-#else
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      float f[VEC]; x.p[i].unpack(f);     // packets past the end are zero
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) ss += f[j] * f[j];
-    }
-#endif
     ss = block_reduce<THREADS>(ss, SumOp(), 0.f, red);
   }
   const float rstd = 1.0f / sqrtf(ss * inv_m + eps);
@@ -209,7 +176,6 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
       x.p[i].unpack(f);
       ld_param(W + (size_t)v * VEC).unpack(w);
       if constexpr (LAYER) ld_param(Bias + (size_t)v * VEC).unpack(b);
-#if TYLO_NORM_F32X2
       if constexpr (LAYER) {
         // ((x - mean) rstd) w + b on pairs: (x + (-mean)) * (rstd w) + b
         const uint64_t nmean2 = sm100::pack_f32x2(-mean, -mean), rstd2 = sm100::pack_f32x2(rstd, rstd);
@@ -227,13 +193,6 @@ norm_fwd_kernel(T* __restrict__ Y, const T* __restrict__ X, const T* __restrict_
           sm100::unpack_f32x2(sm100::mul_f32x2(sm100::pack_f32x2(f[j], f[j + 1]), a2), f[j], f[j + 1]);
         }
       }
-#else
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        if constexpr (LAYER) f[j] = (f[j] - mean) * rstd * w[j] + b[j];
-        else f[j] = f[j] * rstd * (w[j] + offset);
-      }
-#endif
       x.p[i].pack(f);
     }
   }
