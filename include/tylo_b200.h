@@ -254,6 +254,25 @@ int32_t tylo_b200_decode_combine(void* O, float* O_merged, float* M_merged, floa
  * 8*Hkv*B blocks, decode.jl:163,187). */
 int32_t tylo_b200_decode_suggest_splits(int32_t Sk, int32_t Hkv, int32_t B);
 
+/* decode_attention in ONE launch (same arguments as tylo_b200_decode_attention plus `tickets`): the
+ * split kernel's CTAs count themselves off per (kv head, batch); the last one of a group of eight
+ * splits folds the group, the last group merges the groups (mha_decode_combine's algebra,
+ * decode.jl:119-140) and writes O — no second kernel (decode.jl:187-209 launches two).
+ * `tickets`: tylo_b200_decode_ticket_count(n_splits, Hkv, B) int32 words of device memory, zeroed
+ * once by the caller; every call leaves them zero again.  Calls that share a ticket buffer (or the
+ * partial buffers) must not overlap on the GPU.  Q, K, V must not be the output of a decode launch of
+ * this library directly ahead on the same stream (the kernel starts reading them while such a launch
+ * is still finishing).  With tickets == NULL, fp32 storage, head dims other than 64/128 or more than
+ * 16 query heads per kv head the call is tylo_b200_decode_attention (two launches). */
+int64_t tylo_b200_decode_ticket_count(int32_t n_splits, int32_t Hkv, int32_t B);
+int32_t tylo_b200_decode_attention_fused(void* O, const void* Q, const void* K, const void* V,
+                                         const int32_t* lengths,
+                                         float* O_partial, float* M_partial, float* L_partial,
+                                         int32_t* tickets, int32_t n_splits,
+                                         int32_t Dk, int32_t Dv, int32_t Sk,
+                                         int32_t H, int32_t Hkv, int32_t B,
+                                         int32_t dtype, tylo_stream_t stream);
+
 /* decode_attention for callers that cannot supply scratch.  This entry has no counterpart in the
  * reference (there the scratch is always a caller-owned array, decode.jl:164,223-231).
  *
@@ -305,6 +324,22 @@ int32_t tylo_b200_decode_exchange(void* O, const float* O_partial, const float* 
                                   int32_t Dv, int32_t H, int32_t B, int32_t dtype,
                                   int64_t timeout_us, tylo_stream_t stream);
 int32_t tylo_b200_decode_exchange_status(void* own_buffer, int32_t* code);
+
+/* The sharded step in ONE launch per GPU: tylo_b200_decode_attention_fused on this GPU's key range
+ * (`lengths_local` = live keys inside it, `Sk_local` = its allocated length) whose last CTA per
+ * (kv head, batch) does what tylo_b200_decode_exchange does for the heads of that group: push the merged
+ * record to every peer, raise the flags, wait (bounded by `timeout_us`, same status word) and merge the
+ * `world` records into O.  Same receive buffers, same call counters: the two forms can be mixed call by
+ * call as long as every rank makes the same sequence.  Falls back to split + exchange (two launches)
+ * where the fused form does not apply (see tylo_b200_decode_attention_fused). */
+int32_t tylo_b200_decode_attention_sharded(void* O, const void* Q, const void* K, const void* V,
+                                           const int32_t* lengths_local,
+                                           float* O_partial, float* M_partial, float* L_partial,
+                                           int32_t* tickets, int32_t n_splits,
+                                           void* const* peer_buffers, int32_t rank, int32_t world,
+                                           int32_t Dk, int32_t Dv, int32_t Sk_local,
+                                           int32_t H, int32_t Hkv, int32_t B, int32_t dtype,
+                                           int64_t timeout_us, tylo_stream_t stream);
 
 /* Device buffers visible to every process of the node (CUDA IPC).  alloc: cudaMalloc + zero fill;
  * export: writes tylo_b200_peer_handle_bytes() opaque bytes to pass to the other processes by any

@@ -55,6 +55,14 @@ def test_argument_validation_without_device(tylo):
     # decode: n_splits must be positive
     rc = lib.tylo_b200_decode_attention(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), 0, 64, 64, 128, 4, 4, 1, 0, None)
     assert rc == 1
+    # one-launch decode: same checks, and a rank outside the world is refused
+    rc = lib.tylo_b200_decode_attention_fused(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), f(9), 0, 64, 64, 128, 4, 4, 1, 1, None)
+    assert rc == 1
+    peers = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    rc = lib.tylo_b200_decode_attention_sharded(f(1), f(2), f(3), f(4), f(5), f(6), f(7), f(8), f(9), 4, peers, 2, 2,
+                                                64, 64, 128, 4, 4, 1, 1, 0, None)
+    assert rc == 1 and b"rank" in lib.tylo_b200_last_error()
+    assert lib.tylo_b200_decode_ticket_count(148, 8, 1) == 8 * (19 + 1)
     # unknown dtype is rejected before any launch
     assert lib.tylo_b200_softmax_fwd(_fake(), _fake(2), 8, 8, 7, None) == 1
 

@@ -30,9 +30,30 @@ def test_decode_vs_reference(tylo, oracle, case, dt):
     K, K64 = draw(rng, (B, Hkv, Sk, Dk), dt)
     V, V64 = draw(rng, (B, Hkv, Sk, Dv), dt)
     ln = torch.tensor(lengths, dtype=torch.int32, device="cuda")
-    O = torch.full((B, H, Dv), float("nan"), dtype=Q.dtype, device="cuda")
-    tylo.decode_attention_(O, Q, K, V, lengths=ln, n_splits=n_splits)
-    check(O, oracle.decode_reference(Q64, K64, V64, lengths), dt, "decode")
+    ref = oracle.decode_reference(Q64, K64, V64, lengths)
+    for one_launch in (True, False):                       # the split kernel finishing the merge itself, or two launches
+        O = torch.full((B, H, Dv), float("nan"), dtype=Q.dtype, device="cuda")
+        tylo.decode_attention_(O, Q, K, V, lengths=ln, n_splits=n_splits, one_launch=one_launch)
+        check(O, ref, dt, f"decode (one_launch={one_launch})")
+
+
+@pytest.mark.parametrize("n_splits", [1, 7, 8, 9, 37, 148])
+def test_one_launch_ticket_groups(tylo, oracle, n_splits):
+    """The one-launch form over split counts around its group size of eight (one group, a partial group,
+    many groups), repeated on one scratch: the ticket words must be left at zero by every call."""
+    rng = np.random.default_rng(n_splits)
+    B, H, Hkv, Sk, D = 2, 16, 2, 5000, 128
+    Q, Q64 = draw(rng, (B, H, D), "bf16"); K, K64 = draw(rng, (B, Hkv, Sk, D), "bf16"); V, V64 = draw(rng, (B, Hkv, Sk, D), "bf16")
+    lengths = [5000, 3]
+    ln = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    ref = oracle.decode_reference(Q64, K64, V64, lengths)
+    O = torch.empty_like(Q)
+    sc = tylo.allocate_scratchspace_decode_attention(O, Q, n_splits=n_splits)
+    for _ in range(3):
+        O.fill_(float("nan"))
+        tylo.decode_attention_(O, Q, K, V, lengths=ln, scratch=sc)
+        check(O, ref, "bf16", f"one-launch decode, {n_splits} splits")
+        assert int(sc.tickets.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])

@@ -29,8 +29,9 @@ def _shard(t, K, V, lengths, r, world):
     return K[:, :, b:e].contiguous(), V[:, :, b:e].contiguous(), ll
 
 
+@pytest.mark.parametrize("one_launch", [True, False], ids=["one-launch", "two-launch"])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
-def test_single_rank_exchange_equals_decode(tylo, oracle, dt):
+def test_single_rank_exchange_equals_decode(tylo, oracle, dt, one_launch):
     rng = np.random.default_rng(3)
     B, H, Hkv, Sk, D = 2, 16, 4, 1024, 128
     Q, Q64 = draw(rng, (B, H, D), dt); K, K64 = draw(rng, (B, Hkv, Sk, D), dt); V, V64 = draw(rng, (B, Hkv, Sk, D), dt)
@@ -43,15 +44,17 @@ def test_single_rank_exchange_equals_decode(tylo, oracle, dt):
         sc = tylo.allocate_scratchspace_decode_attention(O, Q, n_splits=6)
         for _ in range(3):                      # the call counter in the buffer advances per call
             O.fill_(float("nan"))
-            tylo.sharded_decode_attention_(O, Q, K, V, lengths_local=ln, exchange=ex, scratch=sc)
+            tylo.sharded_decode_attention_(O, Q, K, V, lengths_local=ln, exchange=ex, scratch=sc, one_launch=one_launch)
             assert ex.status() == 0
             check(O, ref, dt, "single-rank exchange")
+            assert int(sc.tickets.abs().sum()) == 0        # every counter is back at zero for the next call
     finally:
         ex.close()
 
 
+@pytest.mark.parametrize("one_launch", [True, False], ids=["one-launch", "two-launch"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_ranks_in_turn_merge_and_bounded_wait(tylo, oracle, world):
+def test_ranks_in_turn_merge_and_bounded_wait(tylo, oracle, world, one_launch):
     rng = np.random.default_rng(world)
     B, H, Hkv, Sk, D = 2, 8, 2, 2048, 64
     dt = "bf16"
@@ -60,14 +63,16 @@ def test_ranks_in_turn_merge_and_bounded_wait(tylo, oracle, world):
     ref = oracle.decode_reference(Q64, K64, V64, lengths)
     group = tylo.DecodeExchange.local_group(B, H, D, world=world, timeout_us=20_000)
     shards = [_shard(tylo, K, V, lengths, r, world) for r in range(world)]
-    scs = [tylo.allocate_scratchspace_decode_attention(torch.empty_like(Q), Q, n_splits=4) for _ in range(world)]
+    # 11 splits per shard: two ticket groups (8 + 3) in the one-launch form
+    scs = [tylo.allocate_scratchspace_decode_attention(torch.empty_like(Q), Q, n_splits=11) for _ in range(world)]
     try:
         for order in (list(range(world)), list(reversed(range(world)))):   # two calls: both record parities
             for i, r in enumerate(order):
                 Kr, Vr, lr = shards[r]
                 O = torch.full_like(Q, 7.0)
                 t0 = time.time()
-                tylo.sharded_decode_attention_(O, Q, Kr, Vr, lengths_local=lr, exchange=group[r], scratch=scs[r])
+                tylo.sharded_decode_attention_(O, Q, Kr, Vr, lengths_local=lr, exchange=group[r], scratch=scs[r],
+                                               one_launch=one_launch)
                 if i < world - 1:
                     # peers have not pushed: the wait must run out, be reported, and O stay untouched
                     with pytest.raises(tylo.TyloError) as e:

@@ -70,6 +70,8 @@ _lib.tylo_b200_device_status.restype = c_int32
 _lib.tylo_b200_device_status.argtypes = [POINTER(c_int32)]
 _lib.tylo_b200_decode_suggest_splits.restype = c_int32
 _lib.tylo_b200_decode_suggest_splits.argtypes = [c_int32] * 3
+_lib.tylo_b200_decode_ticket_count.restype = c_int64
+_lib.tylo_b200_decode_ticket_count.argtypes = [c_int32] * 3
 _lib.tylo_b200_decode_exchange_bytes.restype = c_int64
 _lib.tylo_b200_decode_exchange_bytes.argtypes = [c_int32] * 4
 _lib.tylo_b200_peer_handle_bytes.restype = c_int32
@@ -87,6 +89,8 @@ _SIGS = {
     "tylo_b200_flex_attention_bwd": [_ptr] * 13 + [_i64, POINTER(_MaskDesc), POINTER(_ScoreDesc)] + [_i32] * 8 + [_f32, _i32, _i32, _ptr],
     "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
+    "tylo_b200_decode_attention_fused": [_ptr] * 9 + [_i32] * 8 + [_ptr],
+    "tylo_b200_decode_attention_sharded": [_ptr] * 9 + [_i32, POINTER(c_void_p)] + [_i32] * 9 + [_i64, _ptr],
     "tylo_b200_decode_combine": [_ptr] * 7 + [_i32, _i64, _i64] + [_i32] * 4 + [_ptr],
     "tylo_b200_decode_exchange": [_ptr] * 4 + [_i32, _i64, _i64, POINTER(c_void_p)] + [_i32] * 6 + [_i64, _ptr],
     "tylo_b200_decode_exchange_status": [_ptr, POINTER(c_int32)],
@@ -850,6 +854,7 @@ class DecodeScratch(NamedTuple):
     O_partial: torch.Tensor   # (n_splits, B, H, Dv) fp32
     M_partial: torch.Tensor   # (n_splits, B, H) fp32
     L_partial: torch.Tensor
+    tickets: Optional[torch.Tensor] = None   # int32 counters of the one-launch form, zeroed once (the kernels put them back)
 
 
 def decode_suggest_splits(Sk: int, Hkv: int, B: int) -> int:
@@ -860,8 +865,10 @@ def allocate_scratchspace_decode_attention(O, Q, *, n_splits=8) -> DecodeScratch
     """allocate_scratchspace(decode_attention!, O, Q; n_splits) (decode.jl:223-231)."""
     B, H, Dv = O.shape
     f = dict(dtype=torch.float32, device=O.device)
+    # ticket words for any kv-head count up to H (the library indexes them by (kv head, batch))
+    nt = int(_lib.tylo_b200_decode_ticket_count(int(n_splits), H, B))
     return DecodeScratch(torch.empty(n_splits, B, H, Dv, **f), torch.empty(n_splits, B, H, **f),
-                         torch.empty(n_splits, B, H, **f))
+                         torch.empty(n_splits, B, H, **f), torch.zeros(max(nt, 1), dtype=torch.int32, device=O.device))
 
 
 def _decode_dims(O, Q, K, V):
@@ -874,9 +881,11 @@ def _decode_dims(O, Q, K, V):
     return B, H, Hkv, Sk, Dk, Dv
 
 
-def decode_attention_(O, Q, K, V, *, lengths, n_splits=8, scratch=None):
+def decode_attention_(O, Q, K, V, *, lengths, n_splits=8, scratch=None, one_launch=True):
     """decode_attention!(O, Q, K, V; lengths, n_splits, scratch) -> O (decode.jl:158-212).
-    ``n_splits=None`` asks the library for a count that fills the GPU."""
+    ``n_splits=None`` asks the library for a count that fills the GPU.  With ``one_launch`` (and a scratch
+    that carries ticket words) the split kernel also merges; otherwise split and merge are two launches as
+    in the reference."""
     B, H, Hkv, Sk, Dk, Dv = _decode_dims(O, Q, K, V)
     if scratch is not None:
         n_splits = scratch.O_partial.shape[0]
@@ -887,6 +896,11 @@ def decode_attention_(O, Q, K, V, *, lengths, n_splits=8, scratch=None):
     if lengths.dtype != torch.int32:
         raise TypeError("lengths must be int32")
     _dense(O, Q, K, V, lengths, *scratch)
+    if one_launch and len(scratch) > 3 and scratch.tickets is not None:
+        _check(_lib.tylo_b200_decode_attention_fused(_p(O), _p(Q), _p(K), _p(V), _p(lengths), _p(scratch.O_partial),
+                                                     _p(scratch.M_partial), _p(scratch.L_partial), _p(scratch.tickets),
+                                                     n_splits, Dk, Dv, Sk, H, Hkv, B, _dtype(Q), _stream()))
+        return O
     _check(_lib.tylo_b200_decode_attention(_p(O), _p(Q), _p(K), _p(V), _p(lengths), _p(scratch.O_partial),
                                            _p(scratch.M_partial), _p(scratch.L_partial), n_splits, Dk, Dv, Sk, H,
                                            Hkv, B, _dtype(Q), _stream()))
@@ -908,7 +922,7 @@ def decode_combine_(O, O_partial, M_partial, L_partial, *, n_splits, o_stride, m
     dt = _dtype(O) if O is not None else (F32 if dtype is None else dtype)
     mo = mm = ml = None
     if merged is not None:
-        mo, mm, ml = merged
+        mo, mm, ml = merged[:3]
     _check(_lib.tylo_b200_decode_combine(_p(O), _p(mo), _p(mm), _p(ml), _p(O_partial), _p(M_partial), _p(L_partial),
                                          int(n_splits), int(o_stride), int(ml_stride), Dv, H, B, dt, _stream()))
 
@@ -1001,11 +1015,25 @@ class DecodeExchange:
             self._own = None
 
 
-def sharded_decode_attention_(O, Q, K_local, V_local, *, lengths_local, exchange: DecodeExchange, scratch):
-    """decode_attention! with the keys of every sequence sharded over ranks: split kernel on the local
-    keys (``lengths_local`` = live keys inside this rank's range), then one exchange launch."""
-    decode_split_(Q, K_local, V_local, lengths=lengths_local, scratch=scratch)
-    return exchange.exchange_(O, scratch)
+SHARDED_DECODE_LAUNCHES = 1      # kernels per sharded decode step in the one-launch form
+
+
+def sharded_decode_attention_(O, Q, K_local, V_local, *, lengths_local, exchange: DecodeExchange, scratch,
+                              one_launch=True):
+    """decode_attention! with the keys of every sequence sharded over ranks (``lengths_local`` = live keys
+    inside this rank's range).  One launch: the split kernel's last CTA per (kv head, batch) merges the local
+    splits, pushes the record to every peer and merges theirs.  ``one_launch=False``: split kernel, then the
+    exchange kernel (two launches)."""
+    if not (one_launch and len(scratch) > 3 and scratch.tickets is not None):
+        decode_split_(Q, K_local, V_local, lengths=lengths_local, scratch=scratch)
+        return exchange.exchange_(O, scratch)
+    B, H, Hkv, Sk, Dk, Dv = _decode_dims(O, Q, K_local, V_local)
+    _dense(O, Q, K_local, V_local, lengths_local, *scratch)
+    _check(_lib.tylo_b200_decode_attention_sharded(
+        _p(O), _p(Q), _p(K_local), _p(V_local), _p(lengths_local), _p(scratch.O_partial), _p(scratch.M_partial),
+        _p(scratch.L_partial), _p(scratch.tickets), scratch.O_partial.shape[0], exchange._peers, exchange.rank,
+        exchange.world, Dk, Dv, Sk, H, Hkv, B, _dtype(Q), exchange.timeout_us, _stream()))
+    return O
 
 
 # ---------------------------------------------------------------------------------------------

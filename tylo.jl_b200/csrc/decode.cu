@@ -13,7 +13,6 @@
 // merged once at the end and the CTA writes one (normalised O, max, sum) partial.
 //
 // A scalar fp32 kernel covers fp32 storage and any shape the tensor path does not.
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -68,6 +67,197 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
+// ---- one-launch tail ---------------------------------------------------------------------------------
+// With a ticket buffer the split kernel also finishes the job: CTAs draw a ticket per group of kGroup
+// consecutive splits of their (kv head, batch); the CTA that completes a group folds the group's partials
+// into one (written over the group's first slot), then draws a second-level ticket; the CTA that
+// completes the last group merges the group partials and writes O — or, when the sequence is sharded
+// over GPUs, pushes the merged record to every peer, waits (bounded) for theirs and merges those.
+// The merge algebra is mha_decode_combine's (decode.jl:119-140).  Every counter is put back to zero by
+// the CTA that completes it, so a zeroed buffer stays valid from call to call.
+constexpr int kGroup = 8;
+
+struct DecodeTail {
+  int32_t* tickets;              // null: write the partials only
+  void* O;                       // (Dv, H, B) in the storage type
+  ExchangePeers peers;           // receive buffers of all ranks (world > 1)
+  int rank, world;
+  unsigned long long timeout_ns;
+};
+
+__host__ __device__ inline int decode_groups(int n_splits) { return (n_splits + kGroup - 1) / kGroup; }
+
+// One warp merges `count` partials of head `hb` (slots first, first + step, ...): lane owns VEC = D / 32
+// adjacent columns.  All loads of a round are independent; they go to L2 (written by other CTAs).
+template <int D>
+__device__ __forceinline__ void merge_slots(const float* Op, const float* Mp, const float* Lp, size_t BH, size_t hb,
+                                            int first, int step, int count, int lane, float (&o)[D / 32], float& m_out,
+                                            float& l_out) {
+  constexpr int VEC = D / 32;
+  float m = -INFINITY;
+  for (int k = lane; k < count; k += 32) m = fmaxf(m, __ldcg(Mp + (size_t)(first + k * step) * BH + hb));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  float l = 0.f;
+  for (int k0 = 0; k0 < count; k0 += kGroup) {
+    float ms[kGroup], ls[kGroup], val[kGroup][VEC];
+#pragma unroll
+    for (int u = 0; u < kGroup; ++u) {
+      const bool live = k0 + u < count;
+      const size_t slot = ((size_t)(first + (live ? k0 + u : 0) * step)) * BH + hb;
+      ms[u] = live ? __ldcg(Mp + slot) : -INFINITY;
+      ls[u] = live ? __ldcg(Lp + slot) : 0.f;
+      if (VEC == 4) {
+        const float4 t = live ? __ldcg(reinterpret_cast<const float4*>(Op + slot * D) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        val[u][0] = t.x; val[u][1] = t.y; val[u][VEC - 2] = t.z; val[u][VEC - 1] = t.w;
+      } else {
+        const float2 t = live ? __ldcg(reinterpret_cast<const float2*>(Op + slot * D) + lane) : make_float2(0.f, 0.f);
+        val[u][0] = t.x; val[u][1] = t.y;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kGroup; ++u) {
+      const float w = (ms[u] == -INFINITY) ? 0.f : ls[u] * exp2f(ms[u] - m);
+      l += w;
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] += w * val[u][v];
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) o[v] = acc[v] * inv;
+  m_out = m; l_out = l;
+}
+
+// The same merge over the records the ranks of a sharded sequence have pushed into this GPU's receive
+// buffer: record r starts `stride` words after record r - 1 and holds D values, the max and the sum.
+template <int D>
+__device__ __forceinline__ void merge_records(const float* recs, int64_t stride, int count, int lane, float (&o)[D / 32],
+                                              float& m_out, float& l_out) {
+  constexpr int VEC = D / 32;
+  float m = -INFINITY;
+  for (int r = 0; r < count; ++r) m = fmaxf(m, __ldcg(recs + r * stride + D));
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  float l = 0.f;
+#pragma unroll 4
+  for (int r = 0; r < count; ++r) {
+    const float* rec = recs + r * stride;
+    const float mr = __ldcg(rec + D), lr = __ldcg(rec + D + 1);
+    const float w = (mr == -INFINITY) ? 0.f : lr * exp2f(mr - m);
+    l += w;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] += w * __ldcg(rec + lane * VEC + v);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) o[v] = acc[v] * inv;
+  m_out = m; l_out = l;
+}
+
+template <int D>
+__device__ __forceinline__ void store_row(float* dst, int lane, const float (&o)[D / 32]) {
+  if (D / 32 == 4) reinterpret_cast<float4*>(dst)[lane] = make_float4(o[0], o[1], o[D / 32 - 2], o[D / 32 - 1]);
+  else reinterpret_cast<float2*>(dst)[lane] = make_float2(o[0], o[1]);
+}
+
+// Tail of one (kv head, batch) CTA after its own partial is in memory.  Uniform over the CTA.
+template <typename T, int D, int NWARPS>
+__device__ __forceinline__ void decode_tail(const DecodeTail& tail, float* Op, float* Mp, float* Lp, int n_splits,
+                                            int split, int hkb, int b, int hk, int H, int B, int G) {
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_groups = decode_groups(n_splits);
+  const int gi = split / kGroup;
+  const int gfirst = gi * kGroup;
+  const int gsz = min(kGroup, n_splits - gfirst);
+  int32_t* tk = tail.tickets + (size_t)hkb * (n_groups + 1);
+  const size_t BH = (size_t)B * H;
+
+  // ---- level 1: the CTA that completes its group folds the group into slot `gfirst` --------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&tk[gi], 1);
+    s_last = (t == gsz - 1);
+    if (s_last) tk[gi] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (gsz > 1) {
+    for (int g = warp; g < G; g += NWARPS) {
+      const size_t hb = (size_t)b * H + (size_t)hk * G + g;
+      float o[D / 32], m, l;
+      merge_slots<D>(Op, Mp, Lp, BH, hb, gfirst, 1, gsz, lane, o, m, l);
+      __syncwarp();
+      const size_t slot = (size_t)gfirst * BH + hb;
+      store_row<D>(Op + slot * D, lane, o);
+      if (lane == 0) { Mp[slot] = m; Lp[slot] = l; }
+    }
+  }
+
+  // ---- level 2: the CTA that completes the last group merges the group partials -----------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&tk[n_groups], 1);
+    s_last = (t == n_groups - 1);
+    if (s_last) tk[n_groups] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  T* O = static_cast<T*>(tail.O);
+  const int world = tail.world, rank = tail.rank;
+  const ExchangeLayout lay = exchange_layout(world, (int)BH, D);
+  for (int g = warp; g < G; g += NWARPS) {
+    const size_t hb = (size_t)b * H + (size_t)hk * G + g;
+    float o[D / 32], m, l;
+    merge_slots<D>(Op, Mp, Lp, BH, hb, 0, kGroup, n_groups, lane, o, m, l);
+    if (world > 1) {
+      // push this GPU's record of the head to every rank (its own buffer included), then the flags
+      uint32_t* self = reinterpret_cast<uint32_t*>(tail.peers.buf[rank]);
+      const uint32_t epoch = self[lay.epoch_off + hb] + 1u;     // call counter of this head
+      const int par = (int)(epoch & 1u);
+      for (int p = 0; p < world; ++p) {
+        float* rec = tail.peers.buf[p] + lay.data_off + ((int64_t)(par * world + rank) * (int64_t)BH + (int64_t)hb) * lay.rec;
+        store_row<D>(rec, lane, o);
+        if (lane == 0) *reinterpret_cast<float2*>(rec + D) = make_float2(m, l);
+      }
+      __threadfence_system();      // every lane's peer stores are ordered before the flags raised below
+      __syncwarp();
+      bool ok = true;
+      if (lane < world) {
+        st_release_sys(reinterpret_cast<uint32_t*>(tail.peers.buf[lane]) + lay.flag_off + (int64_t)rank * (int64_t)BH + (int64_t)hb, epoch);
+        const uint32_t* f = self + lay.flag_off + (int64_t)lane * (int64_t)BH + (int64_t)hb;
+        const unsigned long long t0 = global_ns();
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {          // bounded wait for rank `lane`'s record
+          if (global_ns() - t0 > tail.timeout_ns) { ok = false; break; }
+          __nanosleep(64);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        // a peer never arrived: record it, keep the call counter in step, leave O untouched
+        if (lane == 0) { atomicMax(self, 1u + (uint32_t)hb); self[lay.epoch_off + hb] = epoch; }
+        continue;
+      }
+      const float* recs = tail.peers.buf[rank] + lay.data_off + ((int64_t)par * world * (int64_t)BH + (int64_t)hb) * lay.rec;
+      merge_records<D>(recs, (int64_t)BH * lay.rec, world, lane, o, m, l);
+      if (lane == 0) self[lay.epoch_off + hb] = epoch;
+    }
+    // output in the storage type
+    T* dst = O + hb * D + lane * (D / 32);
+#pragma unroll
+    for (int v = 0; v < D / 32; ++v) dst[v] = Elem<T>::from_f(o[v]);
+  }
+}
+
 // ---- tensor path ----------------------------------------------------------------------------------
 // grid.x = n_splits * Hkv * B, split fastest.  G16: query group of 9..16 heads (rows 8..15 live).
 template <typename T, int D, int TN, int NWARPS, int STAGES, bool G16>
@@ -75,7 +265,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
 decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                         const int32_t* __restrict__ lengths, float* __restrict__ Op,
                         float* __restrict__ Mp, float* __restrict__ Lp, int Sk, int H, int Hkv, int B,
-                        int G, int n_splits, int split_size, float scale_log2) {
+                        int G, int n_splits, int split_size, float scale_log2,
+                        const __grid_constant__ DecodeTail tail) {
   constexpr int ROW_BYTES = D * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;          // 16-byte chunks per row
   constexpr int TILE_BYTES = TN * ROW_BYTES;      // one K (or V) tile
@@ -87,8 +278,11 @@ decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const 
   static_assert(WARP_BYTES >= 16 * D * 4 + 128, "merge staging must fit in the warp's ring");
   extern __shared__ __align__(128) uint8_t smem[];
 
-  dependency_wait();         // this kernel may have been placed while the one before it was finishing
-  dependents_may_launch();   // the merge kernel behind this one may be placed while the splits still run
+  // This kernel may have been placed while the launch before it on the stream was still finishing
+  // (programmatic dependent launch).  It streams its keys and values straight away and waits for that
+  // launch only before its first write to memory the two may share (partials, tickets, output): Q, K, V
+  // must therefore not be produced by a decode launch of this library directly ahead on the stream.
+  dependents_may_launch();   // whatever follows may be placed while the splits still run
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x % n_splits;
   const int hkb = blockIdx.x / n_splits;
@@ -261,6 +455,7 @@ decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const 
     }
   }
   __syncthreads();
+  dependency_wait();
 
   // merge the warps and write the split's partial
   for (int idx = threadIdx.x; idx < G * D; idx += NWARPS * 32) {
@@ -282,6 +477,7 @@ decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const 
     Op[hb * D + d] = l > 0.f ? acc / l : 0.f;
     if (d == 0) { Mp[hb] = m; Lp[hb] = l; }
   }
+  if (tail.tickets) decode_tail<T, D, NWARPS>(tail, Op, Mp, Lp, n_splits, split, hkb, b, hk, H, B, G);
 }
 
 // ---- scalar path: any dtype, D <= 512, any G ----------------------------------------------------
@@ -424,7 +620,7 @@ static int decode_split_size(int Sk, int n_splits) {
 template <typename T, int D, int TN, int NWARPS, int STAGES>
 static int32_t launch_decode_mma(const void* Q, const void* K, const void* V, const int32_t* lengths, float* Op,
                                  float* Mp, float* Lp, int n_splits, int Sk, int H, int Hkv, int B,
-                                 cudaStream_t st) {
+                                 const DecodeTail& tail, cudaStream_t st) {
   const int G = H / Hkv;
   const int split_size = decode_split_size(Sk, n_splits);
   const float scale_log2 = kLog2eD / sqrtf((float)D);
@@ -433,51 +629,38 @@ static int32_t launch_decode_mma(const void* Q, const void* K, const void* V, co
   if (G <= 8) {
     auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, false>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 2) != 0, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
+    TYLO_CUDA_OK(launch_overlapped(true, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
                                    (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
-                                   scale_log2));
+                                   scale_log2, tail));
   } else {
     auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, true>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 2) != 0, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
+    TYLO_CUDA_OK(launch_overlapped(true, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
                                    (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
-                                   scale_log2));
+                                   scale_log2, tail));
   }
   return check_launch("decode_split_mma");
 }
 
-static int decode_cfg() {
-  static int cfg = -1;
-  if (cfg < 0) {
-    const char* e = getenv("TYLO_B200_DECODE_CFG");  // tuning aid: 0, 1 or 2
-    cfg = e ? atoi(e) : 0;
-    if (cfg < 0 || cfg > 2) cfg = 0;
-  }
-  return cfg;
+// Whether the tensor-core split kernel (and with it the one-launch tail) covers these extents.
+static bool decode_mma_eligible(int32_t dtype, int Dk, int Dv, int H, int Hkv) {
+  return (dtype == TYLO_BF16 || dtype == TYLO_F16) && Dk == Dv && (Dk == 64 || Dk == 128) && Hkv > 0 && H / Hkv <= 16;
 }
 
 template <typename T>
 static int32_t decode_split_dispatch(const void* Q, const void* K, const void* V, const int32_t* lengths,
                                      float* Op, float* Mp, float* Lp, int n_splits, int Dk, int Dv, int Sk,
-                                     int H, int Hkv, int B, cudaStream_t st) {
+                                     int H, int Hkv, int B, const DecodeTail& tail, cudaStream_t st) {
   const int G = H / Hkv;
   if constexpr (!std::is_same<T, float>::value) {
     if (Dk == Dv && (Dk == 64 || Dk == 128) && G <= 16) {
-      const int cfg = decode_cfg();
-#define TYLO_DEC(D_, TN_, W_, S_) \
-  return launch_decode_mma<T, D_, TN_, W_, S_>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, st)
-      if (Dk == 128) {
-        if (cfg == 0) TYLO_DEC(128, 16, 4, 3);   //  96 KB, two CTAs per SM
-        if (cfg == 1) TYLO_DEC(128, 32, 4, 3);   // 192 KB, one CTA per SM
-        TYLO_DEC(128, 32, 4, 2);                 // 128 KB
-      } else {
-        if (cfg == 0) TYLO_DEC(64, 32, 4, 3);
-        if (cfg == 1) TYLO_DEC(64, 64, 4, 3);
-        TYLO_DEC(64, 32, 4, 2);
-      }
-#undef TYLO_DEC
+      // 16-key tiles at head dim 128 (96 KB of rings, two CTAs per SM), 32-key tiles at 64: the best of the
+      // tile / stage combinations measured (32-key tiles with 3 stages leave one CTA per SM at D 128).
+      if (Dk == 128) return launch_decode_mma<T, 128, 16, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, st);
+      return launch_decode_mma<T, 64, 32, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, st);
     }
   }
+  TYLO_REQUIRE(tail.tickets == nullptr, TYLO_ERR_UNSUPPORTED, "decode: the one-launch form needs the tensor-core split kernel");
   TYLO_REQUIRE(Dk <= 512 && Dv <= 512, TYLO_ERR_UNSUPPORTED, "decode: head dims above 512 are not supported");
   const int split_size = decode_split_size(Sk, n_splits);
   const float scale_log2 = kLog2eD / sqrtf((float)Dk);
@@ -496,7 +679,7 @@ static int32_t decode_combine_dispatch(void* O, float* Om, float* Mm, float* Lm,
   // Many partials per head (long contexts): the 1024-thread block-parallel merge.  Few partials: a small
   // block per head, or a thousand mostly idle threads per head would cost more than the merge itself.
   if (n_splits > 16 && Dv % 4 == 0 && Dv <= 512 && aligned16(Op) && o_stride % 4 == 0) {
-    TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 1) != 0, decode_combine_wide_kernel<T>, dim3(grid), merge_block(Dv),
+    TYLO_CUDA_OK(launch_overlapped(true, decode_combine_wide_kernel<T>, dim3(grid), merge_block(Dv),
                                    merge_smem_floats(1024, Dv) * sizeof(float), st, (T*)O, Om, Mm, Lm, Op, Mp, Lp,
                                    n_splits, o_stride, ml_stride, Dv));
     return check_launch("decode_combine_wide");
@@ -530,9 +713,12 @@ using namespace tylo;
 extern "C" int32_t tylo_b200_decode_suggest_splits(int32_t Sk, int32_t Hkv, int32_t B) {
   if (Sk <= 0 || Hkv <= 0 || B <= 0) return 1;
   const int64_t groups = (int64_t)Hkv * B;
-  // Eight CTAs' worth of work per SM: measured best or equal from 131,072 to 1,048,576 keys per GPU
-  // (one resident wave of two CTAs per SM is 3 % slower on the long sequences and no faster on short ones).
-  const int64_t target = (int64_t)sm_count() * 8;
+  // Eight CTAs' worth of work per SM when that still leaves a split a couple of thousand keys (measured best
+  // from 512 Ki keys per GPU upwards: CTAs that finish early make room for the rest); for shorter caches one
+  // resident wave of two CTAs per SM, whose fixed cost per CTA (start-up, the closing merge) is paid once
+  // (measured on a 131,072-key shard: 83 us against 95 us with eight per SM in the one-launch form).
+  int64_t target = (int64_t)sm_count() * 8;
+  if ((int64_t)Sk * groups < target * 2048) target = (int64_t)sm_count() * 2;
   int64_t n = (target + groups - 1) / groups;
   const int64_t max_by_len = (Sk + 255) / 256;          // keep at least 256 keys per split
   if (n > max_by_len) n = max_by_len;
@@ -549,8 +735,9 @@ extern "C" int32_t tylo_b200_decode_split(const void* Q, const void* K, const vo
   if (int32_t rc = check_decode_dims("decode_split", n_splits, Dk, Dv, Sk, H, Hkv, B)) return rc;
   TYLO_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O_partial), TYLO_ERR_MISALIGNED,
                "decode_split: pointers must be 16-byte aligned");
+  const DecodeTail none{};
   TYLO_DISPATCH_DTYPE(dtype, T, return (decode_split_dispatch<T>(Q, K, V, lengths, O_partial, M_partial, L_partial,
-                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B,
+                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, none,
                                                                  (cudaStream_t)stream)));
   return TYLO_OK;
 }
@@ -590,6 +777,78 @@ extern "C" int32_t tylo_b200_decode_attention(void* O, const void* Q, const void
   if (rc) return rc;
   return tylo_b200_decode_combine(O, nullptr, nullptr, nullptr, O_partial, M_partial, L_partial, n_splits,
                                   (int64_t)H * B * Dv, (int64_t)H * B, Dv, H, B, dtype, stream);
+}
+
+// ---- one launch: split, merge and (for a sharded sequence) the exchange between GPUs ------------------------
+extern "C" int64_t tylo_b200_decode_ticket_count(int32_t n_splits, int32_t Hkv, int32_t B) {
+  if (n_splits <= 0 || Hkv <= 0 || B <= 0) return 0;
+  return (int64_t)Hkv * B * (decode_groups(n_splits) + 1);
+}
+
+static int32_t decode_one_launch(void* O, const void* Q, const void* K, const void* V, const int32_t* lengths,
+                                 float* O_partial, float* M_partial, float* L_partial, int32_t* tickets,
+                                 int32_t n_splits, const ExchangePeers* peers, int rank, int world, int32_t Dk,
+                                 int32_t Dv, int32_t Sk, int32_t H, int32_t Hkv, int32_t B, int32_t dtype,
+                                 int64_t timeout_us, tylo_stream_t stream) {
+  DecodeTail tail{};
+  tail.tickets = tickets; tail.O = O; tail.rank = rank; tail.world = world;
+  if (peers) tail.peers = *peers;
+  tail.timeout_ns = timeout_us > 0 ? (unsigned long long)timeout_us * 1000ull : 2000000000ull;   // default: two seconds
+  TYLO_DISPATCH_DTYPE(dtype, T, return (decode_split_dispatch<T>(Q, K, V, lengths, O_partial, M_partial, L_partial,
+                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, tail,
+                                                                 (cudaStream_t)stream)));
+  return TYLO_OK;
+}
+
+extern "C" int32_t tylo_b200_decode_attention_fused(void* O, const void* Q, const void* K, const void* V,
+                                                    const int32_t* lengths, float* O_partial, float* M_partial,
+                                                    float* L_partial, int32_t* tickets, int32_t n_splits, int32_t Dk,
+                                                    int32_t Dv, int32_t Sk, int32_t H, int32_t Hkv, int32_t B,
+                                                    int32_t dtype, tylo_stream_t stream) {
+  TYLO_REQUIRE(O && Q && K && V && lengths && O_partial && M_partial && L_partial, TYLO_ERR_INVALID_ARGUMENT,
+               "decode_attention_fused: all pointers must be non-null");
+  if (int32_t rc = check_decode_dims("decode_attention_fused", n_splits, Dk, Dv, Sk, H, Hkv, B)) return rc;
+  TYLO_REQUIRE(aligned16(O) && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O_partial), TYLO_ERR_MISALIGNED,
+               "decode_attention_fused: pointers must be 16-byte aligned");
+  if (!tickets || !decode_mma_eligible(dtype, Dk, Dv, H, Hkv))    // shapes of the scalar kernel: two launches
+    return tylo_b200_decode_attention(O, Q, K, V, lengths, O_partial, M_partial, L_partial, n_splits, Dk, Dv, Sk, H,
+                                      Hkv, B, dtype, stream);
+  return decode_one_launch(O, Q, K, V, lengths, O_partial, M_partial, L_partial, tickets, n_splits, nullptr, 0, 1, Dk,
+                           Dv, Sk, H, Hkv, B, dtype, 0, stream);
+}
+
+extern "C" int32_t tylo_b200_decode_attention_sharded(void* O, const void* Q, const void* K, const void* V,
+                                                      const int32_t* lengths_local, float* O_partial, float* M_partial,
+                                                      float* L_partial, int32_t* tickets, int32_t n_splits,
+                                                      void* const* peer_buffers, int32_t rank, int32_t world,
+                                                      int32_t Dk, int32_t Dv, int32_t Sk_local, int32_t H, int32_t Hkv,
+                                                      int32_t B, int32_t dtype, int64_t timeout_us,
+                                                      tylo_stream_t stream) {
+  TYLO_REQUIRE(O && Q && K && V && lengths_local && O_partial && M_partial && L_partial && peer_buffers,
+               TYLO_ERR_INVALID_ARGUMENT, "decode_attention_sharded: all pointers must be non-null");
+  if (int32_t rc = check_decode_dims("decode_attention_sharded", n_splits, Dk, Dv, Sk_local, H, Hkv, B)) return rc;
+  TYLO_REQUIRE(world >= 1 && world <= kMaxExchangeWorld, TYLO_ERR_UNSUPPORTED,
+               "decode_attention_sharded: world size %d outside 1..%d", world, kMaxExchangeWorld);
+  TYLO_REQUIRE(rank >= 0 && rank < world, TYLO_ERR_INVALID_ARGUMENT, "decode_attention_sharded: rank %d outside 0..%d",
+               rank, world - 1);
+  TYLO_REQUIRE(aligned16(O) && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O_partial), TYLO_ERR_MISALIGNED,
+               "decode_attention_sharded: pointers must be 16-byte aligned");
+  if (!tickets || !decode_mma_eligible(dtype, Dk, Dv, H, Hkv)) {
+    // two launches: the split kernel, then the exchange kernel
+    if (int32_t rc = tylo_b200_decode_split(Q, K, V, lengths_local, O_partial, M_partial, L_partial, n_splits, Dk, Dv,
+                                            Sk_local, H, Hkv, B, dtype, stream))
+      return rc;
+    return tylo_b200_decode_exchange(O, O_partial, M_partial, L_partial, n_splits, (int64_t)H * B * Dv, (int64_t)H * B,
+                                     peer_buffers, rank, world, Dv, H, B, dtype, timeout_us, stream);
+  }
+  ExchangePeers peers{};
+  for (int r = 0; r < world; ++r) {
+    TYLO_REQUIRE(peer_buffers[r] && aligned16(peer_buffers[r]), TYLO_ERR_INVALID_ARGUMENT,
+                 "decode_attention_sharded: peer buffer %d is null or not 16-byte aligned", r);
+    peers.buf[r] = static_cast<float*>(peer_buffers[r]);
+  }
+  return decode_one_launch(O, Q, K, V, lengths_local, O_partial, M_partial, L_partial, tickets, n_splits, &peers, rank,
+                           world, Dk, Dv, Sk_local, H, Hkv, B, dtype, timeout_us, stream);
 }
 
 // ---- decode without caller-provided scratch ------------------------------------------------------------

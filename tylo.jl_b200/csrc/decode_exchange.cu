@@ -23,37 +23,6 @@
 
 namespace tylo {
 
-constexpr int kMaxExchangeWorld = 16;
-struct ExchangePeers { float* buf[kMaxExchangeWorld]; };
-
-struct ExchangeLayout {   // offsets in 4-byte words from the start of a rank's buffer
-  int64_t epoch_off, flag_off, data_off, total;
-  int rec;                // words per record: Dv values, max, sum, padded to a multiple of 4
-};
-__host__ __device__ inline ExchangeLayout exchange_layout(int world, int HB, int Dv) {
-  ExchangeLayout l;
-  l.rec = (Dv + 2 + 3) & ~3;
-  l.epoch_off = 16;                                            // words 0..15: status word + reserved
-  l.flag_off = l.epoch_off + ((HB + 15) & ~15);
-  l.data_off = l.flag_off + (((int64_t)world * HB + 15) & ~15);
-  l.total = l.data_off + (int64_t)2 * world * HB * l.rec;
-  return l;
-}
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
 // One CTA of 1024 threads per (head, batch); see merge_partials for the thread layout.
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -119,7 +88,7 @@ static int32_t decode_exchange_dispatch(void* O, const float* Op, const float* M
                                         cudaStream_t st) {
   const unsigned grid = (unsigned)((int64_t)H * B);
   const size_t smem = (size_t)merge_smem_floats(1024, Dv) * sizeof(float);
-  TYLO_CUDA_OK(launch_overlapped((overlap_mask() & 1) != 0, decode_exchange_kernel<T>, dim3(grid), merge_block(Dv), smem, st, (T*)O, Op, Mp, Lp,
+  TYLO_CUDA_OK(launch_overlapped(true, decode_exchange_kernel<T>, dim3(grid), merge_block(Dv), smem, st, (T*)O, Op, Mp, Lp,
                                  n_splits, o_stride, ml_stride, Dv, H * B, peers, rank, world, timeout_ns));
   return check_launch("decode_exchange");
 }

@@ -2,7 +2,6 @@
 // as a block-parallel reduction.  Used for the splits of one GPU and, once more, for the per-GPU records
 // of a sharded sequence.
 #pragma once
-#include <cstdlib>
 
 #include "common.cuh"
 
@@ -69,6 +68,39 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ o_base,
   m_out = mg; l_out = lg;
 }
 
+// ---- exchange of merged records between the GPUs of a node (sharded decode) ---------------------------
+constexpr int kMaxExchangeWorld = 16;
+struct ExchangePeers { float* buf[kMaxExchangeWorld]; };
+
+struct ExchangeLayout {   // offsets in 4-byte words from the start of a rank's buffer
+  int64_t epoch_off, flag_off, data_off, total;
+  int rec;                // words per record: Dv values, max, sum, padded to a multiple of 4
+};
+__host__ __device__ inline ExchangeLayout exchange_layout(int world, int HB, int Dv) {
+  ExchangeLayout l;
+  l.rec = (Dv + 2 + 3) & ~3;
+  l.epoch_off = 16;                                            // words 0..15: status word + reserved
+  l.flag_off = l.epoch_off + ((HB + 15) & ~15);
+  l.data_off = l.flag_off + (((int64_t)world * HB + 15) & ~15);
+  l.total = l.data_off + (int64_t)2 * world * HB * l.rec;
+  return l;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+
 // Programmatic dependent launch: a merge kernel is launched while the split kernel before it on the
 // stream is still running, so its launch latency and CTA placement overlap the split kernel's tail.
 // dependency_wait() returns once the preceding kernel has finished and its writes are visible; it
@@ -76,16 +108,6 @@ __device__ __forceinline__ void merge_partials(const float* __restrict__ o_base,
 // side; it is a no-op when the next launch does not ask for overlap.
 __device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
-
-// TYLO_B200_DECODE_OVERLAP (tuning aid): bit 0 = merge kernels, bit 1 = split kernel; default 3.
-inline int overlap_mask() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("TYLO_B200_DECODE_OVERLAP");
-    v = e ? atoi(e) & 3 : 3;
-  }
-  return v;
-}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_overlapped(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -28,24 +28,32 @@ function decode_attention!(O, Q, K, V; lengths, tensorcore = nothing, TILE_N = 6
         scratch = allocate_scratchspace(decode_attention!, O, Q; n_splits)
     end
     (; O_partial, M_partial, L_partial) = scratch
+    tickets = get(scratch, :tickets, nothing)      # scratch from older code has none: two launches then
     ns = size(O_partial, 4)
     eltype(lengths) === Int32 || throw(ArgumentError("lengths must be Int32"))
-    require_dense(O, Q, K, V, lengths, O_partial, M_partial, L_partial)
-    check(ccall((:tylo_b200_decode_attention, libtylo), Int32,
-        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+    require_dense(O, Q, K, V, lengths, O_partial, M_partial, L_partial, tickets)
+    # one launch: the split kernel's last block per (kv head, batch) merges the partials itself
+    check(ccall((:tylo_b200_decode_attention_fused, libtylo), Int32,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
          Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Ptr{Cvoid}),
         devptr(O), devptr(Q), devptr(K), devptr(V), devptr(lengths), devptr(O_partial), devptr(M_partial),
-        devptr(L_partial), Int32(ns), Int32(Dk), Int32(Dv), Int32(Sk), Int32(H), Int32(Hkv), Int32(B),
+        devptr(L_partial), devptr(tickets), Int32(ns), Int32(Dk), Int32(Dv), Int32(Sk), Int32(H), Int32(Hkv), Int32(B),
         tylo_dtype(eltype(Q)), current_stream()))
     return O
 end
 
-"`(; O_partial (Dv,H,B,n_splits), M_partial, L_partial (H,B,n_splits))`, all `Float32`."
+"""
+`(; O_partial (Dv,H,B,n_splits), M_partial, L_partial (H,B,n_splits))`, all `Float32`, as in the reference,
+plus `tickets`: zeroed `Int32` counters of the one-launch form (the kernels leave them zero; one scratch must
+not serve two calls that overlap on the GPU).
+"""
 function allocate_scratchspace(::typeof(decode_attention!), O, Q; n_splits = 8)
     Dv, H, B = size(O)
+    nt = ccall((:tylo_b200_decode_ticket_count, libtylo), Int64, (Int32, Int32, Int32), n_splits, H, B)
     return (; O_partial = similar(O, Float32, (Dv, H, B, n_splits)),
               M_partial = similar(O, Float32, (H, B, n_splits)),
-              L_partial = similar(O, Float32, (H, B, n_splits)))
+              L_partial = similar(O, Float32, (H, B, n_splits)),
+              tickets = fill!(similar(O, Int32, (max(nt, 1),)), 0))
 end
 
 # ---- one sequence's keys sharded over the GPUs of a node (no counterpart in the reference) ------------
@@ -101,28 +109,25 @@ end
 """
     sharded_decode_attention!(O, Q, K_local, V_local; lengths_local, exchange, scratch) -> O
 
-`decode_attention!` when this process holds only a key range of every sequence: the split kernel on
-the local keys, then one launch that merges the local splits, exchanges the merged records with all
-peers over NVLink and writes the final `O` on every rank.  All ranks call it in the same order.
+`decode_attention!` when this process holds only a key range of every sequence, in one launch: the
+split kernel on the local keys, whose last block per (kv head, batch) merges the local splits, pushes
+the merged record to every peer over NVLink, waits (bounded) for theirs and writes the final `O` on
+every rank.  All ranks call it in the same order.
 """
 function sharded_decode_attention!(O, Q, K, V; lengths_local, exchange::DecodeExchange, scratch)
     Dk, Sk, Hkv, B = size(K)
     Dv, H, _ = size(O)
     (; O_partial, M_partial, L_partial) = scratch
+    tickets = get(scratch, :tickets, nothing)
     ns = size(O_partial, 4)
-    require_dense(O, Q, K, V, lengths_local, O_partial, M_partial, L_partial)
-    check(ccall((:tylo_b200_decode_split, libtylo), Int32,
-        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
-         Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Ptr{Cvoid}),
-        devptr(Q), devptr(K), devptr(V), devptr(lengths_local), devptr(O_partial), devptr(M_partial),
-        devptr(L_partial), Int32(ns), Int32(Dk), Int32(Dv), Int32(Sk), Int32(H), Int32(Hkv), Int32(B),
-        tylo_dtype(eltype(Q)), current_stream()))
-    check(ccall((:tylo_b200_decode_exchange, libtylo), Int32,
-        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int32, Int64, Int64, Ptr{Ptr{Cvoid}},
-         Int32, Int32, Int32, Int32, Int32, Int32, Int64, Ptr{Cvoid}),
-        devptr(O), devptr(O_partial), devptr(M_partial), devptr(L_partial), Int32(ns), Int64(H * B * Dv),
-        Int64(H * B), exchange.peers, exchange.rank, exchange.world, Int32(Dv), Int32(H), Int32(B),
-        tylo_dtype(eltype(O)), exchange.timeout_us, current_stream()))
+    require_dense(O, Q, K, V, lengths_local, O_partial, M_partial, L_partial, tickets)
+    check(ccall((:tylo_b200_decode_attention_sharded, libtylo), Int32,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+         Int32, Ptr{Ptr{Cvoid}}, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int64, Ptr{Cvoid}),
+        devptr(O), devptr(Q), devptr(K), devptr(V), devptr(lengths_local), devptr(O_partial), devptr(M_partial),
+        devptr(L_partial), devptr(tickets), Int32(ns), exchange.peers, exchange.rank, exchange.world, Int32(Dk),
+        Int32(Dv), Int32(Sk), Int32(H), Int32(Hkv), Int32(B), tylo_dtype(eltype(Q)), exchange.timeout_us,
+        current_stream()))
     return O
 end
 
