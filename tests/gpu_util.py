@@ -9,6 +9,11 @@ Tolerances (from the build contract):
                  (the 1e-6 floor covers references that are exactly zero, e.g. a causal
                  query that sees one key has dQ = 0)
   bf16 storage : max-abs <= 2e-2 and mean-abs <= 2e-3 (fp16 is held to the same bound)
+  gradients in 16-bit storage (`scale_hint` given): the same two numbers times
+                 max(1, P / 4), P = the power of two at or above the hint (callers pass max|ref|): a bf16
+                 result in [P/2, P) is spaced P * 2^-8 apart, so its rounding alone reaches P * 2^-9 — 0.016
+                 for values between 4 and 8, before any arithmetic error — and no kernel can meet a fixed
+                 2e-2 on results of that size.  Outputs of magnitude below 4 keep the plain bound.
 """
 from __future__ import annotations
 
@@ -33,6 +38,14 @@ def draw(rng, shape, dt, scale=1.0, shift=0.0):
     return t, back(t)
 
 
+def grad_scale(max_ref) -> float:
+    """Factor on the 16-bit bounds for a result whose largest reference magnitude is `max_ref`:
+    max(1, P / 4) with P the power of two at or above it (1 when no hint is given)."""
+    if max_ref is None or not max_ref > 0:
+        return 1.0
+    return max(1.0, 2.0 ** float(np.ceil(np.log2(max_ref))) / 4.0)
+
+
 def check(got: torch.Tensor, ref: np.ndarray, dt: str, what: str = "", scale_hint: float | None = None):
     g = back(got)
     assert g.shape == ref.shape, f"{what}: shape {g.shape} vs {ref.shape}"
@@ -42,7 +55,6 @@ def check(got: torch.Tensor, ref: np.ndarray, dt: str, what: str = "", scale_hin
         bound = 1e-5 * float(np.abs(ref).max()) + 1e-6
         assert err.max() <= bound, f"{what}: max error {err.max():.3e} > {bound:.3e} (1e-5 relative)"
     else:
-        # gradients that sum many terms are compared relative to their own magnitude
-        s = 1.0 if scale_hint is None else max(1.0, scale_hint)
+        s = grad_scale(scale_hint)
         assert err.max() <= 2e-2 * s, f"{what}: max-abs error {err.max():.3e} > {2e-2 * s:.1e}"
         assert err.mean() <= 2e-3 * s, f"{what}: mean-abs error {err.mean():.3e} > {2e-3 * s:.1e}"

@@ -125,5 +125,5 @@ def test_backward_over_the_listed_blocks(tylo, oracle, dt, agree):
         aQ, aK, aV, _ = o.flex_bwd_ref(dO64, Q64, K64, V64, score=okw["score"], mask=omask, input_pos=5)
         assert np.allclose(rQ, aQ) and np.allclose(rK, aK) and np.allclose(rV, aV)
     for got, ref, name in ((dQ, rQ, "dQ"), (dK, rK, "dK"), (dV, rV, "dV")):
-        check(got, ref, dt, f"block walk {name}", scale_hint=float(np.abs(ref).max()) / 4)
+        check(got, ref, dt, f"block walk {name}", scale_hint=float(np.abs(ref).max()))
     assert t.device_status() == 0

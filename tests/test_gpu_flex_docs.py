@@ -49,5 +49,5 @@ def test_document_tiles(tylo, oracle, cuts, extra, dt):
     dQ, dK, dV = t.grad_flex_attention(dO, Q, K, V, O, checkpoints=cp, **kw)
     rQ, rK, rV, _ = o.flex_bwd_ref(dO64, Q64, K64, V64, **okw)
     for got, ref, name in ((dQ, rQ, "dQ"), (dK, rK, "dK"), (dV, rV, "dV")):
-        check(got, ref, dt, f"docs {name}", scale_hint=float(np.abs(ref).max()) / 4)
+        check(got, ref, dt, f"docs {name}", scale_hint=float(np.abs(ref).max()))
     assert t.device_status() == 0

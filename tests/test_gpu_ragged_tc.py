@@ -76,6 +76,6 @@ def test_ragged_backward(tylo, oracle, dt, D, causal):
                                             V64[b:b + 1, :, :n], mask=mask, input_pos=input_pos)
         for got, ref, name in ((Qd.shadow[b:b + 1, :, :live], rQ, "dQ"), (Kd.shadow[b:b + 1, :, :n], rK, "dK"),
                                (Vd.shadow[b:b + 1, :, :n], rV, "dV")):
-            check(got, ref, dt, f"ragged {name}, batch {b}", scale_hint=float(np.abs(ref).max()) / 4)
+            check(got, ref, dt, f"ragged {name}, batch {b}", scale_hint=float(np.abs(ref).max()))
         assert bool((Qd.shadow[b, :, live:] == 0).all()) and bool((Kd.shadow[b, :, n:] == 0).all())
         assert bool((Vd.shadow[b, :, n:] == 0).all())
