@@ -167,7 +167,7 @@ ROWS = dict(softmax=(4096, 32768), norm=(16384, 8192))
 def shrink():
     """--small: same kernels and tile shapes on a few hundred MB, for profiler captures (a capture
     replays each launch dozens of times; the full-size workloads would take minutes per kernel)."""
-    C3.update(B=1); C4.update(B=1, H=4); C5A.update(B=8); C5B.update(S=1 << 17)
+    C3.update(B=1); C4.update(B=1, H=16); C5A.update(B=8); C5B.update(S=1 << 17)
     ROWS.update(softmax=(1024, 32768), norm=(4096, 8192))
 
 

@@ -11,6 +11,15 @@ from test_host import _RbfOp
 pytestmark = pytest.mark.gpu
 
 
+def _check_reduced(got, ref, dt, what):
+    """Gradients that sum a bias-table gradient over every (q, kv) pair (projection, features): each term
+    carries the 16-bit error of the attention backward, so the sum is held to a bound relative to its own
+    largest entry: 1e-2 for 16-bit storage, 1e-4 for fp32 (summation order)."""
+    err = np.abs(back(got) - ref)
+    bound = (1e-4 if dt == "f32" else 1e-2) * float(np.abs(ref).max()) + 1e-6
+    assert err.max() <= bound, f"{what}: max error {err.max():.3e} > {bound:.3e}"
+
+
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("compose", [None, "softcap"])
 def test_pair_feature_score(tylo, oracle, dt, compose):
@@ -42,7 +51,7 @@ def test_pair_feature_score(tylo, oracle, dt, compose):
     dbias = pg[0]                                                                # (B, H, Sq, Sk) gradient of the table
     leaf = d_mod.a if compose else d_mod
     proj_ref = np.einsum("bhqk,pbqk->ph", dbias, phi)
-    check(leaf.pair_proj, proj_ref, dt, "pair projection gradient", scale_hint=2 * float(np.abs(proj_ref).max()))
+    _check_reduced(leaf.pair_proj, proj_ref, dt, "pair projection gradient")
     if not compose:
         # d bias / d d2 = sum_p proj[p, h] * dphi_p/dd2, then d d2 / d qf = 2 (qf - kf)
         e = np.exp(-c * d2)
@@ -50,6 +59,6 @@ def test_pair_feature_score(tylo, oracle, dt, compose):
         g = np.einsum("bhqk,ph,pbqk->bqk", dbias, pr64, dphi_dd2)
         diff = qf64[:, :, None, :] - kf64[:, None, :, :]
         qref = (2 * g[..., None] * diff).sum(2); kref = (-2 * g[..., None] * diff).sum(1)
-        check(leaf.q_features, qref, dt, "pair q-feature gradient", scale_hint=2 * float(np.abs(qref).max()))
-        check(leaf.k_features, kref, dt, "pair k-feature gradient", scale_hint=2 * float(np.abs(kref).max()))
+        _check_reduced(leaf.q_features, qref, dt, "pair q-feature gradient")
+        _check_reduced(leaf.k_features, kref, dt, "pair k-feature gradient")
     assert tylo.device_status() == 0

@@ -1,20 +1,27 @@
 // Flash-attention forward for sm_100a: tcgen05.mma with accumulators in tensor memory, operands
-// staged by TMA into a 128-byte-swizzled shared-memory ring, warp-specialised roles.
+// staged by TMA into a 128-byte-swizzled shared-memory ring, warp-specialised roles, persistent CTAs.
 //
-// One CTA owns 256 query rows of one (head, batch) as two 128-row tiles A and B, and walks the
-// 128-key tiles their masks allow.  The two tiles share every K/V tile and ping-pong on the
-// tensor pipe: while the softmax warpgroup of one tile works, the MMA issuer runs the other's.
+// A work item is two 128-row Q tiles A and B that share every 128-key K/V tile they visit and ping-pong on
+// the tensor pipe: while the softmax warpgroup of one tile works, the MMA issuer runs the other's.  With an
+// even number of query heads per KV head the two tiles are the same 128 query rows of two heads of one group
+// (identical key ranges, so neither idles while the other finishes); otherwise two adjacent row blocks of one
+// head.  One CTA per SM walks its share of the items: under a causal mask a slot pairs the k-th last with the
+// k-th first query block of a head, so every CTA gets the same work; the next item's K, V and Q loads and its
+// first Q K^T products run under the previous item's epilogue.  Launches with no more items than SMs run one
+// item per CTA.
 //
-//   warp 0       TMA producer: Q_A, Q_B once, then K and V tiles through rings (mbarrier full/empty).
+//   warp 0       TMA producer: per item the first K/V tile, both Q tiles, then the remaining K and V tiles
+//                through rings (mbarrier full/empty).
 //   warp 1       MMA issuer (one elected lane), owner of the tensor-memory allocation:
 //                  S_X  = Q_X K_j^T       (both operands from shared memory, 128 x 128 x D)
 //                  O_X += P_X V_j         (P from tensor memory, V MN-major from shared memory)
+//   warps 2,3    work out the CTA's item table once (one item per thread), then idle: they donate their
+//                registers to the softmax warpgroups.
 //   warps 4..7   softmax of tile A, warps 8..11 softmax of tile B: thread r owns query row r
 //                (= TMEM lane r).  Reads S with tcgen05.ld, applies score/mask mods, keeps a running
 //                max / sum in fp32, writes P (bf16/f16) back over the S columns with tcgen05.st,
 //                rescales O in TMEM only when the row max grew by more than 2^8 (lazy rescaling),
-//                and writes the final O, M, L.
-//   warps 2,3    idle (they only donate their registers to the softmax warpgroups).
+//                and writes the final O through shared memory with TMA stores, M and L directly.
 //
 // TMEM columns: [0,128) S_A/P_A, [128,256) S_B/P_B, [256,256+D) O_A, [384,384+D) O_B.
 // No multicast, no clusters.  Every mbarrier wait is bounded; a time-out sets a status word and
@@ -36,6 +43,15 @@ constexpr uint32_t kRuntimeMods = 0x80000000u;  // template value: read the flag
 constexpr int BM = 128, BN = 128;               // rows of one Q tile, keys of one K/V tile
 constexpr int kFwdThreads = 384;
 
+// Slots of a softmax warp's copy of its work item in shared memory.
+enum { WI_B = 0, WI_H, WI_Q0, WI_KLEN, WI_QLIM, WI_KV0, WI_N, WI_RELEASE, WI_WORDS };
+// One entry of the CTA's item table in shared memory: the softmax view of tile A, of tile B, then what the
+// producer and the MMA issuer need.  Filled once per CTA by the two spare warps, one item per thread, so
+// that no role spends its single working thread on index arithmetic between items.
+enum { IT_A = 0, IT_B = WI_WORDS, IT_NTOT = 2 * WI_WORDS, IT_JLO, IT_AS, IT_AE, IT_BS, IT_BE, IT_HK, IT_HEAD, IT_Q0, IT_BATCH,
+       IT_WORDS };
+constexpr int kMaxItems = 40;
+
 template <int D> struct FwdSmem {
   static constexpr int kStages = (D == 128) ? 2 : 4;
   static constexpr int kTile = BM * D * 2;             // bytes of one Q / K / V tile
@@ -45,9 +61,14 @@ template <int D> struct FwdSmem {
   static constexpr int kBars = kV + kStages * kTile;    // 8-byte mbarriers
   static constexpr int Q_FULL = 0, K_FULL = 2, K_EMPTY = K_FULL + kStages, V_FULL = K_EMPTY + kStages,
                        V_EMPTY = V_FULL + kStages, S_FULL = V_EMPTY + kStages, P_FULL = S_FULL + 2,
-                       O_READY = P_FULL + 2, DONE = O_READY + 2, kNumBars = DONE + 1;
+                       O_READY = P_FULL + 2, Q_EMPTY = O_READY + 2, O_FREE = Q_EMPTY + 1, DONE = O_FREE + 2,
+                       kNumBars = DONE + 1;
+  // Q_EMPTY: every Q K^T product of the finished work item has been issued, its Q tiles may be overwritten;
+  // O_FREE: the softmax warpgroup has read the item's accumulator out of tensor memory.
   static constexpr int kMisc = kBars + 8 * kNumBars;    // tmem base, abort flag
-  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kItems = kMisc + 16;             // item table
+  static constexpr int kStage = (kItems + kMaxItems * IT_WORDS * 4 + 1023) / 1024 * 1024;   // 8 softmax warps x 2 KB of output staging
+  static constexpr int kTotal = kStage + 8 * 2048;
   static constexpr int kDynamic = kTotal + 1024;        // slack for manual 1024-byte alignment
 };
 
@@ -89,23 +110,127 @@ __device__ __forceinline__ float softcap(float s, float cap, float inv_cap) {
   return cap * t;
 }
 
+// Bulk tensor store of a shared-memory box (TMA), tracked in the issuing thread's bulk group.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 struct TileRange { int s, e; };  // CTA-local key-tile indices [s, e) a Q tile takes part in
 
-// Softmax / epilogue of one Q tile (one warpgroup, 128 threads).
+// One work item: 256 query rows (tiles A and B) of one (head, batch) and the key tiles they can see.
+struct FwdItem {
+  int b, h, hk, q0;        // batch, query head, KV head, first query row
+  int k_len, q_lim;        // ragged bounds of this batch entry
+  int jlo, n_tot;          // first key tile and number of key tiles walked (union of A and B)
+  TileRange tr[2];         // per Q tile, relative to jlo
+};
+
+
+// A CTA walks several work items.  Slot s of the launch holds one item (small launches) or the pair
+// (k-th last, k-th first) query block of one head — under a causal mask the heaviest with the lightest, so
+// that every slot costs about the same; CTA c takes slots c, c + gridDim.x, ...  Consecutive slots belong
+// to the same head, so the CTAs running at any time share K/V tiles in L2.
+// The two Q tiles of an item share every K/V tile.  With an even number of query heads per KV head they are
+// the SAME 128 query rows of two heads of one group (both see the same key tiles, so neither idles while the
+// other finishes); otherwise two adjacent row blocks of one head.
+struct FwdPlan { int nqt, per_head, n_slots, per_slot, q_step, h_step, rows, heads; };
+__device__ __forceinline__ FwdPlan fwd_plan(const AttnParams& p, int paired) {
+  FwdPlan pl;
+  const bool pair_heads = (p.G % 2) == 0;
+  pl.rows = pair_heads ? BM : 2 * BM;
+  pl.heads = pair_heads ? 2 : 1;
+  pl.q_step = pair_heads ? 0 : BM;
+  pl.h_step = pair_heads ? 1 : 0;
+  pl.nqt = (p.Sq + pl.rows - 1) / pl.rows;
+  pl.per_slot = paired == 2 ? 2 : 1;      // 2: a slot holds a (heavy, light) pair of query blocks
+  pl.per_head = paired == 2 ? (pl.nqt + 1) / 2 : pl.nqt;
+  pl.n_slots = pl.per_head * (p.H / pl.heads) * p.B;
+  return pl;
+}
+// Query block of entry e of slot s, or -1 if the slot has no such entry (middle block of an odd count).
+__device__ __forceinline__ int fwd_slot_block(const FwdPlan& pl, int s, int e, int& hb) {
+  hb = s / pl.per_head;
+  const int k = s % pl.per_head;
+  const int heavy = pl.nqt - 1 - k;
+  if (e == 0) return heavy;
+  return (k == heavy) ? -1 : k;
+}
+
+__device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, const FwdPlan& pl, uint32_t mask_flags, int hb, int qt) {
+  FwdItem it;
+  const int hpb = p.H / pl.heads;
+  it.b = hb / hpb; it.h = (hb % hpb) * pl.heads; it.hk = it.h / p.G; it.q0 = qt * pl.rows;
+  // Ragged batches (attention.jl:25-26,37-46,60): keys at or beyond k_lengths[b] are masked; 64-row
+  // query blocks that start at or beyond q_lengths[b] are skipped and their output rows left untouched.
+  it.k_len = p.Sk; it.q_lim = p.Sq;
+  if (p.k_lengths) { const int v = p.k_lengths[it.b]; it.k_len = v < 0 ? 0 : (v > p.Sk ? p.Sk : v); }
+  if (p.q_lengths) {
+    const int v = p.q_lengths[it.b];
+    const int ql = v < 0 ? 0 : (v > p.Sq ? p.Sq : v);
+    it.q_lim = min(p.Sq, ((ql + 63) / 64) * 64);
+  }
+  // key tiles each Q tile can see, as item-local index ranges over the union
+  int t0[2], t1[2];
+#pragma unroll
+  for (int X = 0; X < 2; ++X) {
+    const int qx = it.q0 + X * pl.q_step;
+    t0[X] = 0; t1[X] = 0;
+    if (qx < it.q_lim) {
+      AttnParams pr = p; pr.mask_flags = mask_flags;
+      int lo, hi;
+      kv_range(pr, qx + p.input_pos, min(qx + BM, p.Sq) - 1 + p.input_pos, it.k_len, &lo, &hi);
+      if (hi > lo) { t0[X] = lo / BN; t1[X] = (hi - 1) / BN + 1; }
+    }
+  }
+  const bool actA = t1[0] > t0[0], actB = t1[1] > t0[1];
+  it.jlo = actA ? (actB ? min(t0[0], t0[1]) : t0[0]) : t0[1];
+  const int jhi = actA ? (actB ? max(t1[0], t1[1]) : t1[0]) : t1[1];
+  it.n_tot = (actA || actB) ? jhi - it.jlo : 0;
+  it.tr[0] = {actA ? t0[0] - it.jlo : 0, actA ? t1[0] - it.jlo : 0};
+  it.tr[1] = {actB ? t0[1] - it.jlo : 0, actB ? t1[1] - it.jlo : 0};
+  return it;
+}
+
+// Rare path of the lazy rescaling, kept out of line so that its registers do not weigh on the tile loop:
+// multiplies this thread's accumulator row (COLS fp32 columns of tensor memory) by f.
+template <int COLS>
+__device__ __noinline__ void scale_accumulator_row(uint32_t to, float f) {
+#pragma unroll 1
+  for (int q = 0; q < COLS / 8; ++q) {
+    uint32_t v[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(to + q * 8) : "memory");
+    tc_wait_ld();
+#pragma unroll
+    for (int t = 0; t < 8; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * f);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(to + q * 8), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+  }
+  tc_wait_st();
+}
+
+// Softmax / epilogue of one Q tile of one work item (one warpgroup, 128 threads).  Returns false when a
+// bounded wait gave up.
 template <typename T, int D, uint32_t MASK, uint32_t SCORE>
-__device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t mask_flags,
-                                             const uint32_t score_flags, const int X, const int q0x, const int jlo,
-                                             const TileRange tr, const int b, const int h, const uint32_t tmem,
-                                             const uint32_t sbase, volatile int* abort_flag, T* __restrict__ O,
-                                             float* __restrict__ Mout, float* __restrict__ Lout, const int k_len,
-                                             const int q_lim) {
-  // k_len: keys of this batch entry that exist (<= Sk); q_lim: rows below it are computed and stored
+__device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t mask_flags,
+                                             const uint32_t score_flags, const int X, volatile const int* wi,
+                                             const uint32_t tmem, const uint32_t sbase, volatile int* abort_flag,
+                                             const CUtensorMap* tmO, float* __restrict__ Mout, float* __restrict__ Lout,
+                                             const int ph0) {
+  // wi: this warp's copy of the work item in shared memory (see WI_*), read where a value is used instead
+  // of being carried in registers through the tile loop, whose 128 scores per thread leave no room;
+  // ph0: key tiles this warpgroup has walked in the CTA's earlier work items (mbarrier phases go on
+  // counting across items).
   using SM = FwdSmem<D>;
   auto bar = [&](int i) { return sbase + SM::kBars + 8 * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wq = warp & 3;                       // TMEM lane quarter this warp may touch
   const int r = wq * 32 + lane;                  // row within the tile
-  const int row = q0x + r, qpos = row + p.input_pos;
   const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
   const uint32_t ts = tmem + lane_off + X * 128;
   const uint32_t to = tmem + lane_off + 256 + X * 128;
@@ -113,22 +238,13 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
   // units of the running max: raw dot products when there is no score mod (c folds the scale),
   // log2-scaled modded scores otherwise
   const float c = modded ? 1.f : p.scale * kLog2e;
-  const float slope = (score_flags & TYLO_SCORE_ALIBI) ? p.slopes[h] : 0.f;
+  const float slope = (score_flags & TYLO_SCORE_ALIBI) ? p.slopes[wi[WI_H]] : 0.f;
   const float inv_cap = 1.f / p.cap;
   int my_doc = 0;
-  if (mask_flags & TYLO_MASK_DOCUMENT) my_doc = p.doc_q[(size_t)b * p.doc_stride + min(qpos, (int)p.Sq - 1 + p.input_pos)];
-  const int n = tr.e - tr.s;
+  if (mask_flags & TYLO_MASK_DOCUMENT)
+    my_doc = p.doc_q[(size_t)wi[WI_B] * p.doc_stride + min(wi[WI_Q0] + r + p.input_pos, (int)p.Sq - 1 + p.input_pos)];
+  const int n = wi[WI_N];
 
-  // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
-  // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
-  // compare per element against the tile-relative start.
-  int row_lo = 0, row_hi = k_len - 1;
-  if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) row_hi = min(row_hi, qpos);
-  if (mask_flags & TYLO_MASK_SLIDING) row_lo = max(row_lo, qpos - p.window);
-  if (mask_flags & TYLO_MASK_PREFIX) row_hi = min(row_hi, p.prefix_len - 1);
-  if (mask_flags & TYLO_MASK_PREFIX_LM) row_hi = min(row_hi, max(qpos, p.prefix_len - 1));
-  const bool row_any = row_hi >= row_lo;
-  const unsigned row_span = row_any ? (unsigned)(row_hi - row_lo) : 0u;
   // soft cap as s * P(s^2) with the constants of the tanh series folded in (see below)
   const float cap_k1 = p.scale * inv_cap;
   const float cap_a0 = cap_k1 * p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
@@ -138,16 +254,19 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
   float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
   bool ok = true;
   for (int i = 0; i < n && ok; ++i) {
-    const int kv0 = (jlo + tr.s + i) * BN;
+    // (read before the wait for S: none of it depends on the scores)
+    const int kv0 = wi[WI_KV0] + i * BN;
+    const int q_lo = wi[WI_Q0] + p.input_pos, q_hi = q_lo + BM - 1;
+    const int k_len_i = wi[WI_KLEN];
     int ids[4] = {0, 0, 0, 0};   // document ids of the tile's keys: lane t holds key q*32 + t
     bool doc_uniform = false;
     if (mask_flags & TYLO_MASK_DOCUMENT) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) ids[q] = p.doc_kv[(size_t)b * p.doc_stride + min(kv0 + q * 32 + lane, p.Sk - 1)];
+      for (int q = 0; q < 4; ++q) ids[q] = p.doc_kv[(size_t)wi[WI_B] * p.doc_stride + min(kv0 + q * 32 + lane, p.Sk - 1)];
       const int id0 = __shfl_sync(0xffffffffu, ids[0], 0);
       doc_uniform = __all_sync(0xffffffffu, ids[0] == id0 && ids[1] == id0 && ids[2] == id0 && ids[3] == id0);
     }
-    ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::S_FULL + X), i & 1, abort_flag, &g_attn_fwd_status, 301));
+    ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::S_FULL + X), (ph0 + i) & 1, abort_flag, &g_attn_fwd_status, 301));
     if (!ok) break;
     tc_fence_after();
     // P = 0 for the whole tile: nothing to load, exponentiate or rescale
@@ -171,11 +290,11 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     tc_wait_ld();
 
     // which tiles need the element-wise mask?
-    const int q_lo = q0x + p.input_pos, q_hi = q0x + BM - 1 + p.input_pos;
-    bool partial = kv0 + BN > k_len;
+    bool partial = kv0 + BN > k_len_i;
     if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING | TYLO_MASK_PREFIX_LM)) partial = partial || (kv0 + BN - 1 > q_lo);
     if (mask_flags & TYLO_MASK_SLIDING) partial = partial || (kv0 < q_hi - p.window);
     if (mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM)) partial = true;
+    if (MASK == kRuntimeMods && p.n_or > 0) partial = true;
     if (mask_flags & TYLO_MASK_DOCUMENT) partial = partial || !doc_uniform || __any_sync(0xffffffffu, ids[0] != my_doc);
     const bool doc_elementwise = (mask_flags & TYLO_MASK_DOCUMENT) && !doc_uniform;
     const bool row_doc_ok = !(mask_flags & TYLO_MASK_DOCUMENT) || doc_elementwise || (__shfl_sync(0xffffffffu, ids[0], 0) == my_doc);
@@ -214,19 +333,50 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
     if (modded && !mods_done) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
+        // BiasScore (mods.jl:219-237): this row's 32 table entries for the chunk, local row index, heads and
+        // batch broadcast by modulo; 16-byte loads when the row start is aligned, guarded scalars otherwise.
+        float bias_row[32];
+        if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) {
+          const int row_b = min(wi[WI_Q0] + r, p.Sq - 1);
+          const float* bp = p.bias + bias_index(p, wi[WI_B], wi[WI_H], row_b, 0);
+          const int kvq = kv0 + q * 32;
+          if ((p.Sk & 3) == 0 && kvq + 32 <= p.Sk) {
+#pragma unroll
+            for (int t = 0; t < 32; t += 4) {
+              const float4 v = __ldg(reinterpret_cast<const float4*>(bp + kvq + t));
+              bias_row[t] = v.x; bias_row[t + 1] = v.y; bias_row[t + 2] = v.z; bias_row[t + 3] = v.w;
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
+          }
+        }
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
           float s = __uint_as_float(sr[q][t]) * p.scale;
           const int kv = kv0 + q * 32 + t;
+          const int qpos = wi[WI_Q0] + r + p.input_pos;
           const bool cap_first = score_flags & TYLO_SCORE_SOFTCAP_FIRST;
           if ((score_flags & TYLO_SCORE_SOFTCAP) && cap_first) s = softcap(s, p.cap, inv_cap);
           if (score_flags & TYLO_SCORE_ALIBI) s = fmaf(slope, (float)(qpos - kv), s);
+          if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) s += bias_row[t];
           if ((score_flags & TYLO_SCORE_SOFTCAP) && !cap_first) s = softcap(s, p.cap, inv_cap);
           sr[q][t] = __float_as_uint(s * kLog2e);
         }
       }
     }
     if (partial) {
+      const int qpos = wi[WI_Q0] + r + p.input_pos;
+  // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
+      // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
+      // compare per element against the tile-relative start.
+      int row_lo = 0, row_hi = wi[WI_KLEN] - 1;
+      if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) row_hi = min(row_hi, qpos);
+      if (mask_flags & TYLO_MASK_SLIDING) row_lo = max(row_lo, qpos - p.window);
+      if (mask_flags & TYLO_MASK_PREFIX) row_hi = min(row_hi, p.prefix_len - 1);
+      if (mask_flags & TYLO_MASK_PREFIX_LM) row_hi = min(row_hi, max(qpos, p.prefix_len - 1));
+      const bool row_any = row_hi >= row_lo;
+      const unsigned row_span = row_any ? (unsigned)(row_hi - row_lo) : 0u;
       // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
       // runtime condition makes the compiler wrap every one of the 128 in a convergence barrier.
       // key kv0 + c is kept iff row_lo <= kv0 + c <= row_hi: (unsigned)(c - rel) <= row_span with
@@ -247,7 +397,36 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
           }
         }
       };
-      if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
+      if (MASK == kRuntimeMods && p.n_or > 0) {
+        // OrMask in disjunctive normal form (mods.jl:164-167): every conjunction of affine terms is one
+        // interval of keys per row; a key is kept if any of them holds it (document terms inside an OR run
+        // on the fp32-arithmetic kernels, see the dispatch).
+        int rels[1 + kMaxOrClauses]; unsigned spans[1 + kMaxOrClauses];
+        rels[0] = rel; spans[0] = row_span;
+#pragma unroll
+        for (int ci = 0; ci < kMaxOrClauses; ++ci) {
+          rels[1 + ci] = 0x40000000; spans[1 + ci] = 0u;
+          if (ci < p.n_or) {
+            const MaskClause& cl = p.or_clause[ci];
+            int lo = 0, hi = wi[WI_KLEN] - 1;
+            if (cl.flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) hi = min(hi, qpos);
+            if (cl.flags & TYLO_MASK_SLIDING) lo = max(lo, qpos - cl.window);
+            if (cl.flags & TYLO_MASK_PREFIX) hi = min(hi, cl.prefix_len - 1);
+            if (cl.flags & TYLO_MASK_PREFIX_LM) hi = min(hi, max(qpos, cl.prefix_len - 1));
+            if (hi >= lo) { rels[1 + ci] = lo - kv0; spans[1 + ci] = (unsigned)(hi - lo); }
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            bool keep = false;
+#pragma unroll
+            for (int ci = 0; ci < 1 + kMaxOrClauses; ++ci) keep = keep || ((unsigned)(q * 32 + t - rels[ci]) <= spans[ci]);
+            sr[q][t] = keep ? sr[q][t] : 0xff800000u;   // -inf
+          }
+        }
+      } else if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
     }
     float mxq[4][2];
 #pragma unroll
@@ -267,28 +446,23 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       pass_empty_tile();
       continue;
     }
-    // lazy rescaling: move the reference max only when it would otherwise overflow the 2^8 headroom
+    // lazy rescaling: move the reference max only when it would otherwise overflow the 2^8 headroom.
+    // A row that has not met an unmasked key yet (m_ref = -inf) has l = 0 and a zero accumulator row: its
+    // reference moves for free.  Only rows that have accumulated something need O and l scaled, which
+    // waits for this tile's previous P V product; that is rare and kept out of line.
     const bool need = (mx > m_ref) && ((m_ref == -INFINITY) || ((mx - m_ref) * c > 8.f));
-    if (__any_sync(0xffffffffu, need)) {
+    const bool scale = need && (m_ref != -INFINITY);
+    if (__any_sync(0xffffffffu, scale)) {
       if (i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::O_READY + X), (i - 1) & 1, abort_flag, &g_attn_fwd_status, 302));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::O_READY + X), (ph0 + i - 1) & 1, abort_flag, &g_attn_fwd_status, 302));
         if (!ok) break;
         tc_fence_after();
-        const float f = need ? ((m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - mx) * c)) : 1.f;
+        const float f = scale ? fast_exp2((m_ref - mx) * c) : 1.f;
         l *= f;
-#pragma unroll
-        for (int q = 0; q < D / 32; ++q) {
-          uint32_t orr[32];
-          tmem_ld32(to + q * 32, orr);
-          tc_wait_ld();
-#pragma unroll
-          for (int t = 0; t < 32; ++t) orr[t] = __float_as_uint(__uint_as_float(orr[t]) * f);
-          tmem_st32(to + q * 32, orr);
-        }
-        tc_wait_st();
+        scale_accumulator_row<D>(to, f);
       }
-      if (need) m_ref = mx;
     }
+    if (need) m_ref = mx;
     const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
     float lsq[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
     // Two scores per instruction on the FMA pipe: fma.rn.f32x2 for the exponent arguments and
@@ -323,32 +497,57 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
   // ---- epilogue: O / l, M, L   (tcgen05.ld is warp-collective: every lane loads, stores are predicated)
   float inv = 0.f;
   if (n > 0 && ok) {
-    ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::O_READY + X), (n - 1) & 1, abort_flag, &g_attn_fwd_status, 303));
+    ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::O_READY + X), (ph0 + n - 1) & 1, abort_flag, &g_attn_fwd_status, 303));
     tc_fence_after();
     inv = l > 0.f ? 1.f / l : 0.f;
   }
   if (ok) {
-    const bool live = row < q_lim;
-    T* og = O + ((size_t)(b * p.H + h) * p.Sq + (live ? row : 0)) * D;
+    const int row = wi[WI_Q0] + r;
+    const bool live = row < wi[WI_QLIM];
+    // The whole accumulator row is read out and packed first, so that the MMA issuer can start the next
+    // work item's P V products while this warpgroup stores.
+    uint4 out[D / 32][4];
 #pragma unroll
     for (int q = 0; q < D / 32; ++q) {
       uint32_t orr[32];
       if (n > 0) { tmem_ld32(to + q * 32, orr); tc_wait_ld(); }
-      uint4 out[4];
-      uint32_t* ow = reinterpret_cast<uint32_t*>(out);
+      uint32_t* ow = reinterpret_cast<uint32_t*>(out[q]);
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
         const float a = (n > 0) ? __uint_as_float(orr[2 * t]) * inv : 0.f;
         const float bb = (n > 0) ? __uint_as_float(orr[2 * t + 1]) * inv : 0.f;
         ow[t] = pack_pair<T>(a, bb);
       }
-      if (live) {
+    }
+    if (wi[WI_RELEASE]) {
+      tc_fence_before();
+      mbar_arrive(bar(SM::O_FREE + X));
+    }
+    // Output rows leave through shared memory: each warp stages 32 rows x 32 columns (2 KB, 64-byte swizzle,
+    // conflict-free 16-byte stores) and one lane hands the box to the TMA unit, which writes whole sectors
+    // and clips rows beyond Sq.  Row-by-row 16-byte stores straight from the registers would touch 32
+    // lines per instruction and hold up every other shared- and global-memory instruction of the SM.
+    // (q_lim is a multiple of 64 and a warp's first row of 32: a warp's rows are all live or all not.)
+    if (__shfl_sync(0xffffffffu, (int)live, 0)) {
+      const uint32_t buf = sbase + SM::kStage + (warp - 4) * 2048;
+      const int row0 = wi[WI_Q0] + wq * 32, bh = wi[WI_B] * p.H + wi[WI_H];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(og + q * 32 + v * 8) = out[v];
+      for (int q = 0; q < D / 32; ++q) {
+        if (lane == 0) bulk_wait_read();          // the box before this one has been read out of the buffer
+        __syncwarp();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint32_t dst = buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(out[q][v].x), "r"(out[q][v].y),
+                       "r"(out[q][v].z), "r"(out[q][v].w) : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) { tma_store_3d(tmO, buf, q * 32, row0, bh); bulk_commit(); }
       }
     }
     if (live) {
-      const size_t si = (size_t)(b * p.H + h) * p.Sq + row;
+      const size_t si = (size_t)(wi[WI_B] * p.H + wi[WI_H]) * p.Sq + row;
       // m_true / m_ref are in units of c; statistics are reported in log2 units (attention!) or
       // natural units (flex)
       const float m2 = (m_true == -INFINITY) ? -INFINITY : m_true * c;
@@ -357,13 +556,15 @@ __device__ __forceinline__ void softmax_tile(const AttnParams& p, const uint32_t
       if (Lout) Lout[si] = lt;
     }
   }
+  return ok;
 }
 
 template <typename T, int D, uint32_t MASK, uint32_t SCORE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                      const __grid_constant__ CUtensorMap tmV, T* __restrict__ O, float* __restrict__ Mout,
-                      float* __restrict__ Lout, const AttnParams p) {
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                      float* __restrict__ Mout,
+                      float* __restrict__ Lout, const AttnParams p, const int paired) {
   using SM = FwdSmem<D>;
   constexpr int ST = SM::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -377,41 +578,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t score_flags = (SCORE == kRuntimeMods) ? p.score_flags : SCORE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nqt = (p.Sq + 2 * BM - 1) / (2 * BM);
-  const int qt = nqt - 1 - (int)(blockIdx.x % nqt);   // heaviest causal tiles first
-  const int hb = blockIdx.x / nqt;
-  const int b = hb / p.H, h = hb % p.H, hk = h / p.G;
-  const int q0 = qt * 2 * BM;
-
-  // Ragged batches (attention.jl:25-26,37-46,60): keys at or beyond k_lengths[b] are masked; 64-row
-  // query blocks that start at or beyond q_lengths[b] are skipped and their output rows left untouched.
-  int k_len = p.Sk, q_lim = p.Sq;
-  if (p.k_lengths) { const int v = p.k_lengths[b]; k_len = v < 0 ? 0 : (v > p.Sk ? p.Sk : v); }
-  if (p.q_lengths) {
-    const int v = p.q_lengths[b];
-    const int ql = v < 0 ? 0 : (v > p.Sq ? p.Sq : v);
-    q_lim = min(p.Sq, ((ql + 63) / 64) * 64);
-  }
-
-  // key tiles each Q tile can see, as CTA-local index ranges over the union
-  int t0[2], t1[2];
-#pragma unroll
-  for (int X = 0; X < 2; ++X) {
-    const int qx = q0 + X * BM;
-    t0[X] = 0; t1[X] = 0;
-    if (qx < q_lim) {
-      AttnParams pr = p; pr.mask_flags = mask_flags;
-      int lo, hi;
-      kv_range(pr, qx + p.input_pos, min(qx + BM, p.Sq) - 1 + p.input_pos, k_len, &lo, &hi);
-      if (hi > lo) { t0[X] = lo / BN; t1[X] = (hi - 1) / BN + 1; }
-    }
-  }
-  const bool actA = t1[0] > t0[0], actB = t1[1] > t0[1];
-  const int jlo = actA ? (actB ? min(t0[0], t0[1]) : t0[0]) : t0[1];
-  const int jhi = actA ? (actB ? max(t1[0], t1[1]) : t1[0]) : t1[1];
-  const int n_tot = (actA || actB) ? jhi - jlo : 0;
-  const TileRange trA = {actA ? t0[0] - jlo : 0, actA ? t1[0] - jlo : 0};
-  const TileRange trB = {actB ? t0[1] - jlo : 0, actB ? t1[1] - jlo : 0};
+  const FwdPlan plan = fwd_plan(p, paired);
+  // items of this CTA: entries e of the slots blockIdx.x, blockIdx.x + gridDim.x, ... (the launch keeps the
+  // count within the table)
+  const int n_local = min(kMaxItems, (plan.n_slots - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x * plan.per_slot);
+  volatile int* tab = reinterpret_cast<volatile int*>(smem + SM::kItems);
 
   if (threadIdx.x == 0) {
     mbar_init(bar(SM::Q_FULL), 1); mbar_init(bar(SM::Q_FULL + 1), 1);
@@ -421,7 +592,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(SM::S_FULL + i), 1); mbar_init(bar(SM::P_FULL + i), 128); mbar_init(bar(SM::O_READY + i), 1);
+      mbar_init(bar(SM::O_FREE + i), 128);
     }
+    mbar_init(bar(SM::Q_EMPTY), 1);
     mbar_init(bar(SM::DONE), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -430,117 +603,181 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     tmem_alloc(smem_addr(tmem_slot), 512);
     tmem_relinquish();
   }
+  if (warp == 2 || warp == 3) {
+    // the item table: thread k of the two spare warps works out item k
+    const int k = threadIdx.x - 64;
+    if (k < n_local) {
+      volatile int* e = tab + k * IT_WORDS;
+      int hb;
+      const int slot = blockIdx.x + (k / plan.per_slot) * gridDim.x;
+      const int qt = fwd_slot_block(plan, slot, k % plan.per_slot, hb);
+      if (qt < 0) {
+        e[IT_NTOT] = -1;                       // no such entry (middle block of an odd count)
+      } else {
+        const FwdItem it = fwd_item(p, plan, mask_flags, hb, qt);
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+          volatile int* w = e + X * WI_WORDS;
+          w[WI_B] = it.b; w[WI_H] = it.h + X * plan.h_step; w[WI_Q0] = it.q0 + X * plan.q_step; w[WI_KLEN] = it.k_len;
+          w[WI_QLIM] = it.q_lim; w[WI_KV0] = (it.jlo + it.tr[X].s) * BN; w[WI_N] = it.tr[X].e - it.tr[X].s;
+          w[WI_RELEASE] = it.n_tot > 0;
+        }
+        e[IT_NTOT] = it.n_tot; e[IT_JLO] = it.jlo; e[IT_AS] = it.tr[0].s; e[IT_AE] = it.tr[0].e; e[IT_BS] = it.tr[1].s;
+        e[IT_BE] = it.tr[1].e; e[IT_HK] = it.hk; e[IT_HEAD] = it.h; e[IT_Q0] = it.q0; e[IT_BATCH] = it.b;
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  // Register split of the 384 x 168 pool: 4 x 32 x 88 + 8 x 32 x 208.  The producer and MMA-issuing
-  // threads are on the latency-critical path of every hand-off: at 56 registers they spill (measured:
-  // 859 TFLOP/s against 944 with 88 on the causal headline shape); the softmax rows fit in 208.
+  // Register split of the 384 x 168 pool: 4 x 32 x 96 + 8 x 32 x 200.  The producer and MMA-issuing
+  // threads are on the latency-critical path of every hand-off and must not spill (measured on the
+  // one-item form: 859 TFLOP/s with 56 registers against 944 with 88); the softmax rows fit in 200 once the
+  // rare accumulator rescale is kept out of line.
+  int k_loaded = 0, v_loaded = 0;   // producer thread only: K and V tiles it has asked for
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp == 0) {
       // ------------------------------------------------------------------ TMA producer
-      if (lane == 0 && n_tot > 0) {
-        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+      if (lane == 0) {
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmO);
+        bool ok = true;
+        int ni = 0, g = 0;   // non-empty items and K/V tiles loaded so far (ring stage and phase)
+        for (int k = 0; k < n_local && ok; ++k) {
+          volatile int* e = tab + k * IT_WORDS;
+          const int n_tot = e[IT_NTOT];
+          if (n_tot <= 0) continue;
+          const int jlo = e[IT_JLO], kvh = e[IT_BATCH] * p.Hkv + e[IT_HK];
+          // One K/V tile of the item: waits for its ring stage, then asks for both halves.
+          auto load_kv = [&](int j) {
+            const int st = g % ST;
+            const int row = (jlo + j) * BN;
+            if (g >= ST) ok = mbar_wait(bar(SM::K_EMPTY + st), ((g / ST) - 1) & 1, abort_flag, &g_attn_fwd_status, 101);
+            if (!ok) return;
+            mbar_expect_tx(bar(SM::K_FULL + st), SM::kTile);
 #pragma unroll
-        for (int X = 0; X < 2; ++X) {
-          if (X == 0 ? actA : actB) {
+            for (int cc = 0; cc < D / 64; ++cc)
+              tma_load_3d(sbase + SM::kK + st * SM::kTile + cc * (BN * 128), &tmK, bar(SM::K_FULL + st), cc * 64, row, kvh);
+            k_loaded = g + 1;
+            if (g >= ST) ok = mbar_wait(bar(SM::V_EMPTY + st), ((g / ST) - 1) & 1, abort_flag, &g_attn_fwd_status, 102);
+            if (!ok) return;
+            mbar_expect_tx(bar(SM::V_FULL + st), SM::kTile);
+#pragma unroll
+            for (int cc = 0; cc < D / 64; ++cc)
+              tma_load_3d(sbase + SM::kV + st * SM::kTile + cc * (BN * 128), &tmV, bar(SM::V_FULL + st), cc * 64, row, kvh);
+            v_loaded = g + 1;
+            ++g;
+          };
+          // The item's first K/V tile goes out before its Q tiles: its ring stage frees a step before the
+          // Q buffers do (those wait for the last Q K^T product of the item before), and the first
+          // product of the new item needs both.
+          load_kv(0);
+          if (!ok) break;
+          // both Q tiles (rows beyond Sq read as zeros), once every Q K^T product of the item before has run
+          if (ni > 0) ok = mbar_wait(bar(SM::Q_EMPTY), (ni - 1) & 1, abort_flag, &g_attn_fwd_status, 103);
+          if (!ok) break;
+#pragma unroll
+          for (int X = 0; X < 2; ++X) {
             mbar_expect_tx(bar(SM::Q_FULL + X), SM::kTile);
 #pragma unroll
             for (int cc = 0; cc < D / 64; ++cc)
-              tma_load_3d(sbase + SM::kQ + X * SM::kTile + cc * (BM * 128), &tmQ, bar(SM::Q_FULL + X), cc * 64, q0 + X * BM,
-                          b * p.H + h);
+              tma_load_3d(sbase + SM::kQ + X * SM::kTile + cc * (BM * 128), &tmQ, bar(SM::Q_FULL + X), cc * 64,
+                          e[IT_Q0] + X * plan.q_step, e[IT_BATCH] * p.H + e[IT_HEAD] + X * plan.h_step);
           }
-        }
-        bool ok = true;
-        for (int j = 0; j < n_tot && ok; ++j) {
-          const int s = j % ST;
-          const int row = (jlo + j) * BN;
-          if (j >= ST) ok = mbar_wait(bar(SM::K_EMPTY + s), ((j / ST) - 1) & 1, abort_flag, &g_attn_fwd_status, 101);
-          if (!ok) break;
-          mbar_expect_tx(bar(SM::K_FULL + s), SM::kTile);
-#pragma unroll
-          for (int cc = 0; cc < D / 64; ++cc)
-            tma_load_3d(sbase + SM::kK + s * SM::kTile + cc * (BN * 128), &tmK, bar(SM::K_FULL + s), cc * 64, row, b * p.Hkv + hk);
-          if (j >= ST) ok = mbar_wait(bar(SM::V_EMPTY + s), ((j / ST) - 1) & 1, abort_flag, &g_attn_fwd_status, 102);
-          if (!ok) break;
-          mbar_expect_tx(bar(SM::V_FULL + s), SM::kTile);
-#pragma unroll
-          for (int cc = 0; cc < D / 64; ++cc)
-            tma_load_3d(sbase + SM::kV + s * SM::kTile + cc * (BN * 128), &tmV, bar(SM::V_FULL + s), cc * 64, row, b * p.Hkv + hk);
+          for (int j = 1; j < n_tot && ok; ++j) load_kv(j);
+          ++ni;
         }
       }
     } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
-      if (lane == 0 && n_tot > 0) {
+      if (lane == 0) {
         constexpr uint32_t idesc_qk = idesc_f16(MmaFmt<T>::v, 0, 0, BM, BN);
         constexpr uint32_t idesc_pv = idesc_f16(MmaFmt<T>::v, 0, 1, BM, D);
-        auto active = [&](int X, int j) { const TileRange& t = X ? trB : trA; return j >= t.s && j < t.e; };
         // Descriptors differ only in their 14-bit start-address field: build the constant upper
         // halves once and add a pre-shifted byte offset per MMA, so that the single issuing thread
         // spends a couple of integer instructions per tcgen05.mma instead of a dependent chain.
         const uint64_t dk_hi = smem_desc_sw128(0, 16, 1024);              // K-major Q / K operands
         const uint64_t dv_hi = smem_desc_sw128(0, BN * 128, 1024);        // MN-major V operand
         auto desc_at = [](uint64_t hi, uint32_t saddr) { return hi | (uint64_t)((saddr & 0x3ffff) >> 4); };
-        auto issue_qk = [&](int X, int j) {
-          const uint32_t d = tmem + X * 128;
-          const uint64_t qd = desc_at(dk_hi, sbase + SM::kQ + X * SM::kTile);
-          const uint64_t kd = desc_at(dk_hi, sbase + SM::kK + (j % ST) * SM::kTile);
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = ((k / 4) * (BM * 128) + (k % 4) * 32) >> 4;   // compile-time constant
-            mma_ss(d, qd + off, kd + off, idesc_qk, k > 0);
-          }
-          tc_commit(bar(SM::S_FULL + X));
-        };
-        auto issue_pv = [&](int X, int j) {
-          const TileRange& t = X ? trB : trA;
-          const uint32_t pa = tmem + X * 128;              // P: 64 columns of packed pairs
-          const uint64_t vd = desc_at(dv_hi, sbase + SM::kV + (j % ST) * SM::kTile);
-          const bool first = (j == t.s);
-#pragma unroll
-          for (int k = 0; k < BN / 16; ++k)
-            mma_ts(tmem + 256 + X * 128, pa + k * 8, vd + (uint32_t)((k * 2048) >> 4), idesc_pv, !first || (k > 0));
-          tc_commit(bar(SM::O_READY + X));
-        };
         bool ok = true;
-        if (actA) ok = ok && mbar_wait(bar(SM::Q_FULL + 0), 0, abort_flag, &g_attn_fwd_status, 201);
-        if (actB) ok = ok && mbar_wait(bar(SM::Q_FULL + 1), 0, abort_flag, &g_attn_fwd_status, 201);
-        ok = ok && mbar_wait(bar(SM::K_FULL + 0), 0, abort_flag, &g_attn_fwd_status, 202);
-        if (ok) {
+        int ni = 0, g0 = 0;      // non-empty items and K/V tiles of the items before this one
+        int cb[2] = {0, 0};      // key tiles each Q tile took part in before this item (S / P / O phases)
+        for (int k = 0; k < n_local && ok; ++k) {
+          volatile int* e = tab + k * IT_WORDS;
+          const int n_tot = e[IT_NTOT];
+          if (n_tot <= 0) continue;
+          const int ts[2] = {e[IT_AS], e[IT_BS]}, te[2] = {e[IT_AE], e[IT_BE]};
+          auto active = [&](int X, int j) { return j >= ts[X] && j < te[X]; };
+          auto issue_qk = [&](int X, int j) {
+            const uint32_t d = tmem + X * 128;
+            const uint64_t qd = desc_at(dk_hi, sbase + SM::kQ + X * SM::kTile);
+            const uint64_t kd = desc_at(dk_hi, sbase + SM::kK + ((g0 + j) % ST) * SM::kTile);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t off = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4;   // compile-time constant
+              mma_ss(d, qd + off, kd + off, idesc_qk, kk > 0);
+            }
+            tc_commit(bar(SM::S_FULL + X));
+          };
+          auto issue_pv = [&](int X, int j) {
+            const uint32_t pa = tmem + X * 128;              // P: 64 columns of packed pairs
+            const uint64_t vd = desc_at(dv_hi, sbase + SM::kV + ((g0 + j) % ST) * SM::kTile);
+            const bool first = (j == ts[X]);
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk)
+              mma_ts(tmem + 256 + X * 128, pa + kk * 8, vd + (uint32_t)((kk * 2048) >> 4), idesc_pv, !first || (kk > 0));
+            tc_commit(bar(SM::O_READY + X));
+          };
+          ok = mbar_wait(bar(SM::Q_FULL + 0), ni & 1, abort_flag, &g_attn_fwd_status, 201);
+          ok = ok && mbar_wait(bar(SM::Q_FULL + 1), ni & 1, abort_flag, &g_attn_fwd_status, 201);
+          ok = ok && mbar_wait(bar(SM::K_FULL + g0 % ST), (g0 / ST) & 1, abort_flag, &g_attn_fwd_status, 202);
+          if (!ok) break;
           tc_fence_after();
           if (active(0, 0)) issue_qk(0, 0);
           if (active(1, 0)) issue_qk(1, 0);
-          tc_commit(bar(SM::K_EMPTY + 0));
-        }
-        for (int j = 0; j < n_tot && ok; ++j) {
-          const int s = j % ST;
-          bool v_ready = false, k_ready = false;
+          tc_commit(bar(SM::K_EMPTY + g0 % ST));
+          if (n_tot == 1) tc_commit(bar(SM::Q_EMPTY));
+          for (int j = 0; j < n_tot && ok; ++j) {
+            const int gj = g0 + j, st = gj % ST;
+            bool v_ready = false, k_ready = false;
 #pragma unroll
-          for (int X = 0; X < 2; ++X) {
-            if (active(X, j)) {
-              if (!v_ready) { ok = mbar_wait(bar(SM::V_FULL + s), (j / ST) & 1, abort_flag, &g_attn_fwd_status, 204); v_ready = true; }
-              const TileRange& t = X ? trB : trA;
-              ok = ok && mbar_wait(bar(SM::P_FULL + X), (j - t.s) & 1, abort_flag, &g_attn_fwd_status, 205);
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv(X, j);
-            }
-            if (j + 1 < n_tot && active(X, j + 1)) {
-              if (!k_ready) {
-                ok = mbar_wait(bar(SM::K_FULL + (j + 1) % ST), ((j + 1) / ST) & 1, abort_flag, &g_attn_fwd_status, 203);
-                k_ready = true;
+            for (int X = 0; X < 2; ++X) {
+              if (active(X, j)) {
+                if (!v_ready) { ok = mbar_wait(bar(SM::V_FULL + st), (gj / ST) & 1, abort_flag, &g_attn_fwd_status, 204); v_ready = true; }
+                // the accumulator of the item before must have been read out before it is overwritten
+                if (j == ts[X] && ni > 0)
+                  ok = ok && mbar_wait(bar(SM::O_FREE + X), (ni - 1) & 1, abort_flag, &g_attn_fwd_status, 206);
+                ok = ok && mbar_wait(bar(SM::P_FULL + X), (cb[X] + j - ts[X]) & 1, abort_flag, &g_attn_fwd_status, 205);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(X, j);
               }
-              if (!ok) break;
-              tc_fence_after();
-              issue_qk(X, j + 1);
+              if (j + 1 < n_tot && active(X, j + 1)) {
+                if (!k_ready) {
+                  ok = mbar_wait(bar(SM::K_FULL + (gj + 1) % ST), ((gj + 1) / ST) & 1, abort_flag, &g_attn_fwd_status, 203);
+                  k_ready = true;
+                }
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(X, j + 1);
+              }
+            }
+            if (!ok) break;
+            tc_commit(bar(SM::V_EMPTY + st));
+            if (j + 1 < n_tot) {
+              tc_commit(bar(SM::K_EMPTY + (gj + 1) % ST));
+              if (j + 2 == n_tot) tc_commit(bar(SM::Q_EMPTY));   // every Q K^T product of the item is issued
             }
           }
-          if (!ok) break;
-          tc_commit(bar(SM::V_EMPTY + s));
-          if (j + 1 < n_tot) tc_commit(bar(SM::K_EMPTY + (j + 1) % ST));
+          // a Q tile without keys in this item: keep in step with its warpgroup's O_FREE phases
+#pragma unroll
+          for (int X = 0; X < 2; ++X)
+            if (ok && ni > 0 && te[X] == ts[X])
+              ok = mbar_wait(bar(SM::O_FREE + X), (ni - 1) & 1, abort_flag, &g_attn_fwd_status, 207);
+          cb[0] += te[0] - ts[0]; cb[1] += te[1] - ts[1];
+          g0 += n_tot; ++ni;
         }
         // nothing may still be executing when the allocation is released
         tc_commit(bar(SM::DONE));
@@ -548,20 +785,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int X = (warp >= 8) ? 1 : 0;
-    softmax_tile<T, D, MASK, SCORE>(p, mask_flags, score_flags, X, q0 + X * BM, jlo, X ? trB : trA, b, h, tmem, sbase,
-                                    abort_flag, O, Mout, Lout, k_len, q_lim);
+    bool ok = true;
+    int ph = 0;      // key tiles this warpgroup walked in earlier items
+    for (int k = 0; k < n_local && ok; ++k) {
+      volatile const int* wi = tab + k * IT_WORDS + X * WI_WORDS;
+      if (tab[k * IT_WORDS + IT_NTOT] < 0) continue;
+      ok = softmax_tile<T, D, MASK, SCORE>(p, mask_flags, score_flags, X, wi, tmem, sbase, abort_flag, &tmO, Mout, Lout, ph);
+      ph += wi[WI_N];
+    }
+    if (lane == 0) bulk_wait_read();      // the last boxes have left the staging buffer
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0 && lane == 0 && n_tot > 0) {
+  if (warp == 0 && lane == 0) {
     // make sure none of this CTA's TMA copies is still in flight before its shared memory is released
-    for (int s = 0; s < ST && s < n_tot; ++s) {
-      const int last = ((n_tot - 1 - s) / ST) * ST + s;   // last tile that used stage s
-      mbar_drain(bar(SM::K_FULL + s), (last / ST) & 1);
-      mbar_drain(bar(SM::V_FULL + s), (last / ST) & 1);
+    for (int s = 0; s < ST; ++s) {
+      // phase of the last tile that used stage s
+      if (s < k_loaded) mbar_drain(bar(SM::K_FULL + s), (((k_loaded - 1 - s) / ST) ) & 1);
+      if (s < v_loaded) mbar_drain(bar(SM::V_FULL + s), (((v_loaded - 1 - s) / ST) ) & 1);
     }
   }
   if (warp == 1) {
@@ -586,6 +830,21 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // 3-D view (D, S, heads*batch) of a dense (D,S,H,B) array; box = 64 x 128 x 1, 128-byte swizzle.
+// Output view for the epilogue's stores: box = 32 columns x 32 rows, 64-byte swizzle.
+static int32_t make_tmap_out(CUtensorMap* map, const void* base, int D, int S, int BH) {
+  auto fn = encode_fn();
+  TYLO_REQUIRE(fn, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TYLO_REQUIRE(r == CUDA_SUCCESS, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+  return TYLO_OK;
+}
+
 static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int BH) {
   auto fn = encode_fn();
   TYLO_REQUIRE(fn, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -608,45 +867,70 @@ bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype) {
 }
 
 template <typename T, int D, uint32_t MASK, uint32_t SCORE>
-static int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* M,
+static int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, float* M,
                           float* L, const AttnParams& p, cudaStream_t st) {
   auto kern = attn_fwd_sm100_kernel<T, D, MASK, SCORE>;
   TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<D>::kDynamic));
-  const long long grid = (long long)((p.Sq + 2 * BM - 1) / (2 * BM)) * p.H * p.B;
-  kern<<<(unsigned)grid, kFwdThreads, FwdSmem<D>::kDynamic, st>>>(mq, mk, mv, (T*)O, M, L, p);
+  // One work item per CTA while the items fit the SMs in one go, and whenever the items' costs cannot be told
+  // in advance (windows, document masks, ragged lengths: the hardware's own CTA scheduling balances those
+  // best — measured on the window + document configuration: 0.337 ms against 0.346 ms).  Otherwise one CTA per
+  // SM, each walking its share of the items with the next item's loads and first products under the previous
+  // item's epilogue; under a causal-type mask a slot pairs a heavy with a light query block, so that every
+  // CTA gets the same amount of work.
+  const bool pair_heads = (p.G % 2) == 0;       // see FwdPlan: two heads of a group, or two row blocks of a head
+  const long long nqt = pair_heads ? (p.Sq + BM - 1) / BM : (p.Sq + 2 * BM - 1) / (2 * BM);
+  const long long heads = pair_heads ? p.H / 2 : p.H;
+  const long long n_items = nqt * heads * p.B;
+  const int sms = sm_count();
+  const bool uneven = (p.mask_flags & (TYLO_MASK_SLIDING | TYLO_MASK_DOCUMENT | TYLO_MASK_PREFIX)) != 0 || p.k_lengths ||
+                      p.q_lengths || p.n_or > 0;
+  int paired = 0;
+  long long grid = n_items;
+  if (n_items > sms && !uneven) {
+    paired = (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_PREFIX_LM)) ? 2 : 1;
+    const long long n_slots = (paired == 2 ? (nqt + 1) / 2 : nqt) * heads * p.B;
+    grid = n_slots < sms ? n_slots : sms;
+    const long long per_cta = kMaxItems / paired;                              // at most kMaxItems items per CTA
+    const long long need = (n_slots + per_cta - 1) / per_cta;
+    if (grid < need) grid = need;
+  }
+  kern<<<(unsigned)grid, kFwdThreads, FwdSmem<D>::kDynamic, st>>>(mq, mk, mv, mo, M, L, p, paired);
   return check_launch("attn_fwd_sm100");
 }
 
 template <typename T, int D>
-static int32_t dispatch_mods(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* M,
+static int32_t dispatch_mods(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, float* M,
                              float* L, const AttnParams& p, cudaStream_t st) {
   constexpr uint32_t C = TYLO_MASK_CAUSAL, W = TYLO_MASK_SLIDING, DOC = TYLO_MASK_DOCUMENT;
   const uint32_t m = p.mask_flags, s = p.score_flags;
+  // OR-ed clauses and bias tables are handled by the variant that reads its flags at run time
+  if (p.n_or > 0 || (s & TYLO_SCORE_BIAS)) return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
   if (s == 0) {
-    if (m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, O, M, L, p, st);
-    if (m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, O, M, L, p, st);
-    if (m == (C | W) || m == W) return launch_fwd<T, D, W, 0>(mq, mk, mv, O, M, L, p, st);
-    if (m == (C | W | DOC) || m == (W | DOC)) return launch_fwd<T, D, W | DOC, 0>(mq, mk, mv, O, M, L, p, st);
+    if (m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (m == (C | W) || m == W) return launch_fwd<T, D, W, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (m == (C | W | DOC) || m == (W | DOC)) return launch_fwd<T, D, W | DOC, 0>(mq, mk, mv, mo, M, L, p, st);
   }
   if (s == TYLO_SCORE_SOFTCAP && (m == (C | W | DOC) || m == (W | DOC)))
-    return launch_fwd<T, D, W | DOC, TYLO_SCORE_SOFTCAP>(mq, mk, mv, O, M, L, p, st);
-  if (s == TYLO_SCORE_SOFTCAP && m == C) return launch_fwd<T, D, C, TYLO_SCORE_SOFTCAP>(mq, mk, mv, O, M, L, p, st);
-  if (s == TYLO_SCORE_ALIBI && m == C) return launch_fwd<T, D, C, TYLO_SCORE_ALIBI>(mq, mk, mv, O, M, L, p, st);
-  return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, O, M, L, p, st);
+    return launch_fwd<T, D, W | DOC, TYLO_SCORE_SOFTCAP>(mq, mk, mv, mo, M, L, p, st);
+  if (s == TYLO_SCORE_SOFTCAP && m == C) return launch_fwd<T, D, C, TYLO_SCORE_SOFTCAP>(mq, mk, mv, mo, M, L, p, st);
+  if (s == TYLO_SCORE_ALIBI && m == C) return launch_fwd<T, D, C, TYLO_SCORE_ALIBI>(mq, mk, mv, mo, M, L, p, st);
+  return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
 }
 
 int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, float* M, float* L, const AttnParams& p,
                        int32_t dtype, cudaStream_t st) {
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
+  if (int32_t rc = make_tmap_out(&mo, O, p.Dv, p.Sq, p.H * p.B)) return rc;
   if (int32_t rc = make_tmap(&mq, Q, p.Dk, p.Sq, p.H * p.B)) return rc;
   if (int32_t rc = make_tmap(&mk, K, p.Dk, p.Sk, p.Hkv * p.B)) return rc;
   if (int32_t rc = make_tmap(&mv, V, p.Dv, p.Sk, p.Hkv * p.B)) return rc;
   if (dtype == TYLO_BF16) {
-    if (p.Dk == 128) return dispatch_mods<__nv_bfloat16, 128>(mq, mk, mv, O, M, L, p, st);
-    return dispatch_mods<__nv_bfloat16, 64>(mq, mk, mv, O, M, L, p, st);
+    if (p.Dk == 128) return dispatch_mods<__nv_bfloat16, 128>(mq, mk, mv, mo, M, L, p, st);
+    return dispatch_mods<__nv_bfloat16, 64>(mq, mk, mv, mo, M, L, p, st);
   }
-  if (p.Dk == 128) return dispatch_mods<__half, 128>(mq, mk, mv, O, M, L, p, st);
-  return dispatch_mods<__half, 64>(mq, mk, mv, O, M, L, p, st);
+  if (p.Dk == 128) return dispatch_mods<__half, 128>(mq, mk, mv, mo, M, L, p, st);
+  return dispatch_mods<__half, 64>(mq, mk, mv, mo, M, L, p, st);
 }
 
 
