@@ -4,14 +4,24 @@
 
 namespace tylo {
 
-// Bias tables, host-built block lists and OR-ed mask clauses run on the fp32-arithmetic kernels only.
+// What the tensor-core kernels leave to the fp32-arithmetic kernels.  Forward: host-built block lists, and
+// OR-ed mask clauses that hold a document term (the tensor-core forward reduces every clause to one interval of
+// keys per row).  Backward: those, every OR-ed mask and bias tables (their gradient is accumulated with atomics
+// there).
+static bool or_with_documents(const AttnParams& p) {
+  if (p.n_or == 0) return false;
+  bool doc = (p.mask_flags & TYLO_MASK_DOCUMENT) != 0;
+  for (int i = 0; i < p.n_or; ++i) doc = doc || (p.or_clause[i].flags & TYLO_MASK_DOCUMENT) != 0;
+  return doc;
+}
+static bool fwd_needs_generic(const AttnParams& p) { return p.bm_count != nullptr || or_with_documents(p); }
 static bool table_mods(const AttnParams& p) {
   return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr || p.n_or > 0;
 }
 
 int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                           const AttnParams& p, int32_t dtype, cudaStream_t st) {
-  if (!table_mods(p) && attn_fwd_sm100_supported(p, dtype)) return attn_fwd_sm100(O, Q, K, V, M, L, p, dtype, st);
+  if (!fwd_needs_generic(p) && attn_fwd_sm100_supported(p, dtype)) return attn_fwd_sm100(O, Q, K, V, M, L, p, dtype, st);
   TYLO_DISPATCH_DTYPE(dtype, T, return attn_fwd_generic<T>(O, Q, K, V, M, L, p, st));
   return TYLO_OK;
 }
