@@ -429,8 +429,12 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
             # (2) every rank's record gathered and merged on the host with the oracle's merge algebra, against
             #     the output the exchange left on this rank.
             o = oracle()
+            # (the one-launch step folds groups of partials in place, so the record is rebuilt here from a
+            # plain split pass over the same keys)
+            vs = t.allocate_scratchspace_decode_attention(O, Q, n_splits=n_splits)
+            t.decode_split_(Q, K, V, lengths=lengths, scratch=vs)
             merged = t.allocate_scratchspace_decode_attention(O, Q, n_splits=1)
-            t.decode_combine_(None, sc.O_partial, sc.M_partial, sc.L_partial, n_splits=n_splits, o_stride=B * H * D,
+            t.decode_combine_(None, vs.O_partial, vs.M_partial, vs.L_partial, n_splits=n_splits, o_stride=B * H * D,
                               ml_stride=B * H, Dv=D, H=H, B=B, merged=merged)
             checks = []
             for h in (0, H - 1):
@@ -465,7 +469,7 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
                 checks.append(parity(O[b:b + 1], ref, f"sequence {b} (length {n}), all {H} heads"))
             return worst(checks)
         w["verify"] = verify
-    w["config"] = dict(workload=("split-KV decode, bf16, 1 sequence x 1,048,576 keys" + (f", KV sharded over {world} GPUs, merged over NVLink by peer stores inside the decode kernels" if world > 1 else ""))
+    w["config"] = dict(workload=("split-KV decode, bf16, 1 sequence x 1,048,576 keys" + (f", KV sharded over {world} GPUs, merged by the library's exchange kernel (peer stores over NVLink, placed under the split kernel's tail)" if world > 1 else ""))
                        if long_ctx else "split-KV decode, bf16, 64 sequences, lengths U[1024,32768]",
                        heads_q=H, heads_kv=Hkv, head_dim=D, n_splits=n_splits, live_kv_bytes=kv_bytes,
                        cuda_graph=w.get("graphed", False))

@@ -215,28 +215,53 @@ __device__ __forceinline__ void decode_tail(const DecodeTail& tail, float* Op, f
   T* O = static_cast<T*>(tail.O);
   const int world = tail.world, rank = tail.rank;
   const ExchangeLayout lay = exchange_layout(world, (int)BH, D);
-  for (int g = warp; g < G; g += NWARPS) {
+  constexpr int kHeadsPerWarp = 16 / NWARPS;      // G <= 16
+  float o[kHeadsPerWarp][D / 32], m[kHeadsPerWarp], l[kHeadsPerWarp];
+  uint32_t epoch[kHeadsPerWarp];
+  uint32_t* self = reinterpret_cast<uint32_t*>(tail.peers.buf[rank]);
+
+  // this GPU's record of each of the warp's heads; with peers, pushed to every rank (its own buffer included)
+#pragma unroll
+  for (int k = 0; k < kHeadsPerWarp; ++k) {
+    const int g = warp + k * NWARPS;
+    if (g >= G) break;
     const size_t hb = (size_t)b * H + (size_t)hk * G + g;
-    float o[D / 32], m, l;
-    merge_slots<D>(Op, Mp, Lp, BH, hb, 0, kGroup, n_groups, lane, o, m, l);
+    merge_slots<D>(Op, Mp, Lp, BH, hb, 0, kGroup, n_groups, lane, o[k], m[k], l[k]);
     if (world > 1) {
-      // push this GPU's record of the head to every rank (its own buffer included), then the flags
-      uint32_t* self = reinterpret_cast<uint32_t*>(tail.peers.buf[rank]);
-      const uint32_t epoch = self[lay.epoch_off + hb] + 1u;     // call counter of this head
-      const int par = (int)(epoch & 1u);
+      epoch[k] = self[lay.epoch_off + hb] + 1u;     // call counter of this head
+      const int par = (int)(epoch[k] & 1u);
       for (int p = 0; p < world; ++p) {
         float* rec = tail.peers.buf[p] + lay.data_off + ((int64_t)(par * world + rank) * (int64_t)BH + (int64_t)hb) * lay.rec;
-        store_row<D>(rec, lane, o);
-        if (lane == 0) *reinterpret_cast<float2*>(rec + D) = make_float2(m, l);
+        store_row<D>(rec, lane, o[k]);
+        if (lane == 0) *reinterpret_cast<float2*>(rec + D) = make_float2(m[k], l[k]);
       }
-      __threadfence_system();      // every lane's peer stores are ordered before the flags raised below
-      __syncwarp();
+    }
+  }
+  if (world > 1) {
+    // One fence for all of the warp's records: every lane's peer stores are ordered before the flags raised
+    // below, then one round of flags and one round of (bounded) waits.
+    __threadfence_system();
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < kHeadsPerWarp; ++k) {
+      const int g = warp + k * NWARPS;
+      if (g >= G) break;
+      const size_t hb = (size_t)b * H + (size_t)hk * G + g;
+      if (lane < world)
+        st_release_sys(reinterpret_cast<uint32_t*>(tail.peers.buf[lane]) + lay.flag_off + (int64_t)rank * (int64_t)BH + (int64_t)hb, epoch[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kHeadsPerWarp; ++k) {
+    const int g = warp + k * NWARPS;
+    if (g >= G) break;
+    const size_t hb = (size_t)b * H + (size_t)hk * G + g;
+    if (world > 1) {
       bool ok = true;
       if (lane < world) {
-        st_release_sys(reinterpret_cast<uint32_t*>(tail.peers.buf[lane]) + lay.flag_off + (int64_t)rank * (int64_t)BH + (int64_t)hb, epoch);
         const uint32_t* f = self + lay.flag_off + (int64_t)lane * (int64_t)BH + (int64_t)hb;
         const unsigned long long t0 = global_ns();
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {          // bounded wait for rank `lane`'s record
+        while ((int32_t)(ld_acquire_sys(f) - epoch[k]) < 0) {          // bounded wait for rank `lane`'s record
           if (global_ns() - t0 > tail.timeout_ns) { ok = false; break; }
           __nanosleep(64);
         }
@@ -244,17 +269,18 @@ __device__ __forceinline__ void decode_tail(const DecodeTail& tail, float* Op, f
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         // a peer never arrived: record it, keep the call counter in step, leave O untouched
-        if (lane == 0) { atomicMax(self, 1u + (uint32_t)hb); self[lay.epoch_off + hb] = epoch; }
+        if (lane == 0) { atomicMax(self, 1u + (uint32_t)hb); self[lay.epoch_off + hb] = epoch[k]; }
         continue;
       }
+      const int par = (int)(epoch[k] & 1u);
       const float* recs = tail.peers.buf[rank] + lay.data_off + ((int64_t)par * world * (int64_t)BH + (int64_t)hb) * lay.rec;
-      merge_records<D>(recs, (int64_t)BH * lay.rec, world, lane, o, m, l);
-      if (lane == 0) self[lay.epoch_off + hb] = epoch;
+      merge_records<D>(recs, (int64_t)BH * lay.rec, world, lane, o[k], m[k], l[k]);
+      if (lane == 0) self[lay.epoch_off + hb] = epoch[k];
     }
     // output in the storage type
     T* dst = O + hb * D + lane * (D / 32);
 #pragma unroll
-    for (int v = 0; v < D / 32; ++v) dst[v] = Elem<T>::from_f(o[v]);
+    for (int v = 0; v < D / 32; ++v) dst[v] = Elem<T>::from_f(o[k][v]);
   }
 }
 

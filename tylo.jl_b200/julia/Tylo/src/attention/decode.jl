@@ -107,18 +107,19 @@ function Base.close(ex::DecodeExchange)
 end
 
 """
-    sharded_decode_attention!(O, Q, K_local, V_local; lengths_local, exchange, scratch) -> O
+    sharded_decode_attention!(O, Q, K_local, V_local; lengths_local, exchange, scratch, one_launch = false) -> O
 
-`decode_attention!` when this process holds only a key range of every sequence, in one launch: the
-split kernel on the local keys, whose last block per (kv head, batch) merges the local splits, pushes
-the merged record to every peer over NVLink, waits (bounded) for theirs and writes the final `O` on
-every rank.  All ranks call it in the same order.
+`decode_attention!` when this process holds only a key range of every sequence.  Default: the split kernel
+on the local keys, then the exchange kernel (placed while the splits still run), which merges the local
+splits, pushes the merged records to every peer over NVLink, waits (bounded) for theirs and writes the final
+`O` on every rank.  `one_launch = true` lets the split kernel's last block per (kv head, batch) do the merge
+and the exchange itself (one launch; measured slower at 2 and 8 GPUs).  All ranks call it in the same order.
 """
-function sharded_decode_attention!(O, Q, K, V; lengths_local, exchange::DecodeExchange, scratch)
+function sharded_decode_attention!(O, Q, K, V; lengths_local, exchange::DecodeExchange, scratch, one_launch = false)
     Dk, Sk, Hkv, B = size(K)
     Dv, H, _ = size(O)
     (; O_partial, M_partial, L_partial) = scratch
-    tickets = get(scratch, :tickets, nothing)
+    tickets = one_launch ? get(scratch, :tickets, nothing) : nothing      # without tickets the library takes two launches
     ns = size(O_partial, 4)
     require_dense(O, Q, K, V, lengths_local, O_partial, M_partial, L_partial, tickets)
     check(ccall((:tylo_b200_decode_attention_sharded, libtylo), Int32,
