@@ -273,6 +273,22 @@ int32_t tylo_b200_decode_attention_fused(void* O, const void* Q, const void* K, 
                                          int32_t H, int32_t Hkv, int32_t B,
                                          int32_t dtype, tylo_stream_t stream);
 
+/* decode_attention over a PAGED KV cache (no counterpart in the reference, whose cache is one dense array
+ * per sequence, decode.jl:158-165; the algorithm is the same split + merge).  K_pages / V_pages are pools of
+ * pages of `page_size` keys, (Dk, page_size, Hkv, n_pages) and (Dv, page_size, Hkv, n_pages) column-major;
+ * block_table is a device int32 (max_pages, B) column-major array: keys [i*page_size, (i+1)*page_size) of
+ * sequence b live in page block_table[i, b].  Only entries below ceil(lengths[b] / page_size) are read.
+ * One launch (tickets as for tylo_b200_decode_attention_fused); 16-bit storage, Dk == Dv in {64, 128}, at most
+ * 16 query heads per kv head, page_size a multiple of 16 keys (32 at head dim 64).  Splits are taken over
+ * page_size * max_pages keys. */
+int32_t tylo_b200_decode_attention_paged(void* O, const void* Q, const void* K_pages, const void* V_pages,
+                                         const int32_t* block_table, const int32_t* lengths,
+                                         float* O_partial, float* M_partial, float* L_partial,
+                                         int32_t* tickets, int32_t n_splits,
+                                         int32_t page_size, int32_t max_pages,
+                                         int32_t Dk, int32_t Dv, int32_t H, int32_t Hkv, int32_t B,
+                                         int32_t dtype, tylo_stream_t stream);
+
 /* decode_attention for callers that cannot supply scratch.  This entry has no counterpart in the
  * reference (there the scratch is always a caller-owned array, decode.jl:164,223-231).
  *

@@ -90,6 +90,7 @@ _SIGS = {
     "tylo_b200_decode_attention": [_ptr] * 8 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_split": [_ptr] * 7 + [_i32] * 8 + [_ptr],
     "tylo_b200_decode_attention_fused": [_ptr] * 9 + [_i32] * 8 + [_ptr],
+    "tylo_b200_decode_attention_paged": [_ptr] * 10 + [_i32] * 9 + [_ptr],
     "tylo_b200_decode_attention_sharded": [_ptr] * 9 + [_i32, POINTER(c_void_p)] + [_i32] * 9 + [_i64, _ptr],
     "tylo_b200_decode_combine": [_ptr] * 7 + [_i32, _i64, _i64] + [_i32] * 4 + [_ptr],
     "tylo_b200_decode_exchange": [_ptr] * 4 + [_i32, _i64, _i64, POINTER(c_void_p)] + [_i32] * 6 + [_i64, _ptr],
@@ -904,6 +905,30 @@ def decode_attention_(O, Q, K, V, *, lengths, n_splits=8, scratch=None, one_laun
     _check(_lib.tylo_b200_decode_attention(_p(O), _p(Q), _p(K), _p(V), _p(lengths), _p(scratch.O_partial),
                                            _p(scratch.M_partial), _p(scratch.L_partial), n_splits, Dk, Dv, Sk, H,
                                            Hkv, B, _dtype(Q), _stream()))
+    return O
+
+
+def paged_decode_attention_(O, Q, K_pages, V_pages, *, block_table, lengths, n_splits=None, scratch=None):
+    """decode_attention! over a paged KV cache: ``K_pages`` / ``V_pages`` are (n_pages, Hkv, page_size, D) pools
+    (Julia's (D, page_size, Hkv, n_pages)), ``block_table`` an int32 (B, max_pages) tensor of page ids,
+    ``lengths`` the live keys per sequence.  One launch."""
+    B, H, Dk = Q.shape
+    n_pages, Hkv, page_size, Dkp = K_pages.shape
+    Dv = V_pages.shape[3]
+    assert Dkp == Dk and tuple(V_pages.shape[:3]) == (n_pages, Hkv, page_size) and tuple(O.shape) == (B, H, Dv)
+    assert block_table.dim() == 2 and block_table.shape[0] == B and H % Hkv == 0
+    if block_table.dtype != torch.int32 or lengths.dtype != torch.int32:
+        raise TypeError("block_table and lengths must be int32")
+    max_pages = int(block_table.shape[1])
+    if scratch is None:
+        if n_splits is None:
+            n_splits = decode_suggest_splits(page_size * max_pages, Hkv, B)
+        scratch = allocate_scratchspace_decode_attention(O, Q, n_splits=n_splits)
+    _dense(O, Q, K_pages, V_pages, block_table, lengths, *scratch)
+    _check(_lib.tylo_b200_decode_attention_paged(
+        _p(O), _p(Q), _p(K_pages), _p(V_pages), _p(block_table), _p(lengths), _p(scratch.O_partial), _p(scratch.M_partial),
+        _p(scratch.L_partial), _p(scratch.tickets), scratch.O_partial.shape[0], page_size, max_pages, Dk, Dv, H, Hkv, B,
+        _dtype(Q), _stream()))
     return O
 
 

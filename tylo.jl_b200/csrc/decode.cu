@@ -85,6 +85,13 @@ struct DecodeTail {
   unsigned long long timeout_ns;
 };
 
+// Paged KV cache: K and V are pools of pages of `page_size` keys, laid out (D, page_size, Hkv, n_pages);
+// sequence b's keys [i * page_size, (i + 1) * page_size) live in page table[b * max_pages + i].
+struct DecodePages {
+  const int32_t* table;          // null: K, V are dense (D, Sk, Hkv, B) arrays
+  int page_size, max_pages;
+};
+
 __host__ __device__ inline int decode_groups(int n_splits) { return (n_splits + kGroup - 1) / kGroup; }
 
 // One warp merges `count` partials of head `hb` (slots first, first + step, ...): lane owns VEC = D / 32
@@ -286,13 +293,13 @@ __device__ __forceinline__ void decode_tail(const DecodeTail& tail, float* Op, f
 
 // ---- tensor path ----------------------------------------------------------------------------------
 // grid.x = n_splits * Hkv * B, split fastest.  G16: query group of 9..16 heads (rows 8..15 live).
-template <typename T, int D, int TN, int NWARPS, int STAGES, bool G16>
+template <typename T, int D, int TN, int NWARPS, int STAGES, bool G16, bool PAGED>
 __global__ void __launch_bounds__(NWARPS * 32)
 decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                         const int32_t* __restrict__ lengths, float* __restrict__ Op,
                         float* __restrict__ Mp, float* __restrict__ Lp, int Sk, int H, int Hkv, int B,
                         int G, int n_splits, int split_size, float scale_log2,
-                        const __grid_constant__ DecodeTail tail) {
+                        const __grid_constant__ DecodeTail tail, const __grid_constant__ DecodePages pages) {
   constexpr int ROW_BYTES = D * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;          // 16-byte chunks per row
   constexpr int TILE_BYTES = TN * ROW_BYTES;      // one K (or V) tile
@@ -324,21 +331,31 @@ decode_split_mma_kernel(const T* __restrict__ Q, const T* __restrict__ K, const 
   const uint32_t wsm_u = smem_u32(wsm);
   const T* kbase_g = K + ((size_t)(b * Hkv + hk) * Sk) * D;
   const T* vbase_g = V + ((size_t)(b * Hkv + hk) * Sk) * D;
+  const int32_t* page_row = PAGED ? pages.table + (size_t)b * pages.max_pages : nullptr;
 
   auto issue = [&](int i) {
     const int tile = warp + i * NWARPS;
     const int kv0 = begin + tile * TN;
     const uint32_t st = wsm_u + (i % STAGES) * STAGE_BYTES;
+    // a tile never straddles pages (page_size is a multiple of the tile): one table look-up per tile
+    const T* kt = kbase_g; const T* vt = vbase_g;
+    int kv_off = 0;
+    if (PAGED) {
+      const int pg = __ldg(page_row + kv0 / pages.page_size);
+      const size_t pbase = ((size_t)pg * Hkv + hk) * pages.page_size * D;
+      kt = K + pbase; vt = V + pbase;
+      kv_off = (kv0 / pages.page_size) * pages.page_size;
+    }
 #pragma unroll
     for (int c = 0; c < TN * CHUNKS / 32; ++c) {
       const int idx = c * 32 + lane;
       const int row = idx / CHUNKS, chunk = idx % CHUNKS;
       const int kv = kv0 + row;
       const bool ok = kv < end;
-      const size_t goff = (size_t)(ok ? kv : begin) * D + chunk * 8;
+      const size_t goff = (size_t)((ok ? kv : kv0) - kv_off) * D + chunk * 8;
       const uint32_t soff = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
-      cp_async16(st + soff, kbase_g + goff, ok);
-      cp_async16(st + TILE_BYTES + soff, vbase_g + goff, ok);
+      cp_async16(st + soff, kt + goff, ok);
+      cp_async16(st + TILE_BYTES + soff, vt + goff, ok);
     }
   };
 
@@ -646,24 +663,25 @@ static int decode_split_size(int Sk, int n_splits) {
 template <typename T, int D, int TN, int NWARPS, int STAGES>
 static int32_t launch_decode_mma(const void* Q, const void* K, const void* V, const int32_t* lengths, float* Op,
                                  float* Mp, float* Lp, int n_splits, int Sk, int H, int Hkv, int B,
-                                 const DecodeTail& tail, cudaStream_t st) {
+                                 const DecodeTail& tail, const DecodePages& pages, cudaStream_t st) {
   const int G = H / Hkv;
   const int split_size = decode_split_size(Sk, n_splits);
   const float scale_log2 = kLog2eD / sqrtf((float)D);
   constexpr int SMEM = NWARPS * STAGES * 2 * TN * D * 2;
   const unsigned grid = (unsigned)((int64_t)n_splits * Hkv * B);
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return e;
+    return launch_overlapped(true, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K, (const T*)V, lengths,
+                             Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size, scale_log2, tail, pages);
+  };
+  const bool paged = pages.table != nullptr;
   if (G <= 8) {
-    auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, false>;
-    TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    TYLO_CUDA_OK(launch_overlapped(true, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
-                                   (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
-                                   scale_log2, tail));
+    if (paged) TYLO_CUDA_OK(go(decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, false, true>));
+    else TYLO_CUDA_OK(go(decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, false, false>));
   } else {
-    auto kern = decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, true>;
-    TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    TYLO_CUDA_OK(launch_overlapped(true, kern, dim3(grid), dim3(NWARPS * 32), SMEM, st, (const T*)Q, (const T*)K,
-                                   (const T*)V, lengths, Op, Mp, Lp, Sk, H, Hkv, B, G, n_splits, split_size,
-                                   scale_log2, tail));
+    if (paged) TYLO_CUDA_OK(go(decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, true, true>));
+    else TYLO_CUDA_OK(go(decode_split_mma_kernel<T, D, TN, NWARPS, STAGES, true, false>));
   }
   return check_launch("decode_split_mma");
 }
@@ -676,17 +694,20 @@ static bool decode_mma_eligible(int32_t dtype, int Dk, int Dv, int H, int Hkv) {
 template <typename T>
 static int32_t decode_split_dispatch(const void* Q, const void* K, const void* V, const int32_t* lengths,
                                      float* Op, float* Mp, float* Lp, int n_splits, int Dk, int Dv, int Sk,
-                                     int H, int Hkv, int B, const DecodeTail& tail, cudaStream_t st) {
+                                     int H, int Hkv, int B, const DecodeTail& tail, const DecodePages& pages,
+                                     cudaStream_t st) {
   const int G = H / Hkv;
   if constexpr (!std::is_same<T, float>::value) {
     if (Dk == Dv && (Dk == 64 || Dk == 128) && G <= 16) {
       // 16-key tiles at head dim 128 (96 KB of rings, two CTAs per SM), 32-key tiles at 64: the best of the
       // tile / stage combinations measured (32-key tiles with 3 stages leave one CTA per SM at D 128).
-      if (Dk == 128) return launch_decode_mma<T, 128, 16, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, st);
-      return launch_decode_mma<T, 64, 32, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, st);
+      if (Dk == 128) return launch_decode_mma<T, 128, 16, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, pages, st);
+      return launch_decode_mma<T, 64, 32, 4, 3>(Q, K, V, lengths, Op, Mp, Lp, n_splits, Sk, H, Hkv, B, tail, pages, st);
     }
   }
   TYLO_REQUIRE(tail.tickets == nullptr, TYLO_ERR_UNSUPPORTED, "decode: the one-launch form needs the tensor-core split kernel");
+  TYLO_REQUIRE(pages.table == nullptr, TYLO_ERR_UNSUPPORTED,
+               "decode: a paged cache needs 16-bit storage, head dim 64 or 128 and at most 16 query heads per kv head");
   TYLO_REQUIRE(Dk <= 512 && Dv <= 512, TYLO_ERR_UNSUPPORTED, "decode: head dims above 512 are not supported");
   const int split_size = decode_split_size(Sk, n_splits);
   const float scale_log2 = kLog2eD / sqrtf((float)Dk);
@@ -762,8 +783,9 @@ extern "C" int32_t tylo_b200_decode_split(const void* Q, const void* K, const vo
   TYLO_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O_partial), TYLO_ERR_MISALIGNED,
                "decode_split: pointers must be 16-byte aligned");
   const DecodeTail none{};
+  const DecodePages dense{};
   TYLO_DISPATCH_DTYPE(dtype, T, return (decode_split_dispatch<T>(Q, K, V, lengths, O_partial, M_partial, L_partial,
-                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, none,
+                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, none, dense,
                                                                  (cudaStream_t)stream)));
   return TYLO_OK;
 }
@@ -815,13 +837,13 @@ static int32_t decode_one_launch(void* O, const void* Q, const void* K, const vo
                                  float* O_partial, float* M_partial, float* L_partial, int32_t* tickets,
                                  int32_t n_splits, const ExchangePeers* peers, int rank, int world, int32_t Dk,
                                  int32_t Dv, int32_t Sk, int32_t H, int32_t Hkv, int32_t B, int32_t dtype,
-                                 int64_t timeout_us, tylo_stream_t stream) {
+                                 int64_t timeout_us, tylo_stream_t stream, const DecodePages& pages = DecodePages{}) {
   DecodeTail tail{};
   tail.tickets = tickets; tail.O = O; tail.rank = rank; tail.world = world;
   if (peers) tail.peers = *peers;
   tail.timeout_ns = timeout_us > 0 ? (unsigned long long)timeout_us * 1000ull : 2000000000ull;   // default: two seconds
   TYLO_DISPATCH_DTYPE(dtype, T, return (decode_split_dispatch<T>(Q, K, V, lengths, O_partial, M_partial, L_partial,
-                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, tail,
+                                                                 n_splits, Dk, Dv, Sk, H, Hkv, B, tail, pages,
                                                                  (cudaStream_t)stream)));
   return TYLO_OK;
 }
@@ -841,6 +863,29 @@ extern "C" int32_t tylo_b200_decode_attention_fused(void* O, const void* Q, cons
                                       Hkv, B, dtype, stream);
   return decode_one_launch(O, Q, K, V, lengths, O_partial, M_partial, L_partial, tickets, n_splits, nullptr, 0, 1, Dk,
                            Dv, Sk, H, Hkv, B, dtype, 0, stream);
+}
+
+extern "C" int32_t tylo_b200_decode_attention_paged(void* O, const void* Q, const void* K_pages, const void* V_pages,
+                                                    const int32_t* block_table, const int32_t* lengths,
+                                                    float* O_partial, float* M_partial, float* L_partial,
+                                                    int32_t* tickets, int32_t n_splits, int32_t page_size,
+                                                    int32_t max_pages, int32_t Dk, int32_t Dv, int32_t H, int32_t Hkv,
+                                                    int32_t B, int32_t dtype, tylo_stream_t stream) {
+  TYLO_REQUIRE(O && Q && K_pages && V_pages && block_table && lengths && O_partial && M_partial && L_partial && tickets,
+               TYLO_ERR_INVALID_ARGUMENT, "decode_attention_paged: all pointers must be non-null");
+  TYLO_REQUIRE(page_size > 0 && max_pages > 0 && (int64_t)page_size * max_pages <= 0x7fffffffLL, TYLO_ERR_INVALID_ARGUMENT,
+               "decode_attention_paged: page_size and max_pages must be positive");
+  const int Sk = page_size * max_pages;          // longest sequence the table can describe
+  if (int32_t rc = check_decode_dims("decode_attention_paged", n_splits, Dk, Dv, Sk, H, Hkv, B)) return rc;
+  TYLO_REQUIRE(decode_mma_eligible(dtype, Dk, Dv, H, Hkv), TYLO_ERR_UNSUPPORTED,
+               "decode_attention_paged: needs 16-bit storage, Dk == Dv in {64, 128} and at most 16 query heads per kv head");
+  TYLO_REQUIRE(page_size % (Dk == 128 ? 16 : 32) == 0, TYLO_ERR_UNSUPPORTED,
+               "decode_attention_paged: page_size (%d) must be a multiple of %d keys", page_size, Dk == 128 ? 16 : 32);
+  TYLO_REQUIRE(aligned16(O) && aligned16(Q) && aligned16(K_pages) && aligned16(V_pages) && aligned16(O_partial),
+               TYLO_ERR_MISALIGNED, "decode_attention_paged: pointers must be 16-byte aligned");
+  DecodePages pages{block_table, page_size, max_pages};
+  return decode_one_launch(O, Q, K_pages, V_pages, lengths, O_partial, M_partial, L_partial, tickets, n_splits, nullptr, 0, 1,
+                           Dk, Dv, Sk, H, Hkv, B, dtype, 0, stream, pages);
 }
 
 extern "C" int32_t tylo_b200_decode_attention_sharded(void* O, const void* Q, const void* K, const void* V,

@@ -1,4 +1,4 @@
-export decode_attention!, sharded_decode_attention!, DecodeExchange, exchange_status
+export decode_attention!, paged_decode_attention!, sharded_decode_attention!, DecodeExchange, exchange_status
 
 "A split count that fills the GPU for this cache (the reference's fixed 8 gives 8·Hkv·B blocks)."
 suggest_splits(Sk, Hkv, B) =
@@ -54,6 +54,40 @@ function allocate_scratchspace(::typeof(decode_attention!), O, Q; n_splits = 8)
               M_partial = similar(O, Float32, (H, B, n_splits)),
               L_partial = similar(O, Float32, (H, B, n_splits)),
               tickets = fill!(similar(O, Int32, (max(nt, 1),)), 0))
+end
+
+"""
+    paged_decode_attention!(O, Q, K_pages, V_pages; block_table, lengths, n_splits = nothing, scratch = …) -> O
+
+`decode_attention!` over a paged KV cache (no counterpart in the reference): `K_pages (Dk, page_size, Hkv, n_pages)`
+and `V_pages (Dv, page_size, Hkv, n_pages)` are pools of pages, `block_table` a device `Int32` `(max_pages, B)`
+matrix of 0-based page ids (keys `[i*page_size, (i+1)*page_size)` of sequence `b` live in page
+`block_table[i+1, b]`), `lengths` the live keys per sequence.  16-bit storage, head dim 64 or 128.
+"""
+function paged_decode_attention!(O, Q, K_pages, V_pages; block_table, lengths, n_splits = nothing, scratch = nothing)
+    Dq, H, B = size(Q)
+    Dk, page_size, Hkv, n_pages = size(K_pages)
+    Dv = size(V_pages, 1)
+    @assert Dq == Dk
+    @assert size(V_pages)[2:4] == (page_size, Hkv, n_pages)
+    @assert size(O) == (Dv, H, B)
+    @assert size(block_table, 2) == B
+    @assert iszero(H % Hkv)
+    max_pages = size(block_table, 1)
+    eltype(block_table) === Int32 && eltype(lengths) === Int32 || throw(ArgumentError("block_table and lengths must be Int32"))
+    if scratch === nothing
+        n_splits === nothing && (n_splits = suggest_splits(page_size * max_pages, Hkv, B))
+        scratch = allocate_scratchspace(decode_attention!, O, Q; n_splits)
+    end
+    (; O_partial, M_partial, L_partial, tickets) = scratch
+    require_dense(O, Q, K_pages, V_pages, block_table, lengths, O_partial, M_partial, L_partial, tickets)
+    check(ccall((:tylo_b200_decode_attention_paged, libtylo), Int32,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+         Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Ptr{Cvoid}),
+        devptr(O), devptr(Q), devptr(K_pages), devptr(V_pages), devptr(block_table), devptr(lengths), devptr(O_partial),
+        devptr(M_partial), devptr(L_partial), devptr(tickets), Int32(size(O_partial, 4)), Int32(page_size), Int32(max_pages),
+        Int32(Dk), Int32(Dv), Int32(H), Int32(Hkv), Int32(B), tylo_dtype(eltype(Q)), current_stream()))
+    return O
 end
 
 # ---- one sequence's keys sharded over the GPUs of a node (no counterpart in the reference) ------------
