@@ -208,6 +208,13 @@ def make_prefill(t, torch, seed, bwd=False, rank=0, world=1, sharded=False):
     pairs_unit = causal_pairs(S) * G
     name = ("prefill_bwd" if bwd else "prefill_fwd") + ("_sharded" if sharded else "")
     w = dict(name=name, unit="TFLOP/s", bound="tensor", scale=1e-12)
+    if not bwd and not sharded and B == 4:
+        # DRAM bytes of one launch of the forward kernel on this very workload (batch 4, one launch per step):
+        # dram__bytes_read.sum 201,601,280 + dram__bytes_write.sum 104,224,768 from a one-launch, three-metric
+        # ncu capture; the algorithmic bytes are 339.7 MB (Q, O 134.2 MB each, K + V 67.1 MB, statistics 4.2 MB),
+        # the difference being output still in L2 when the kernel ends.
+        w["traffic"] = 305826048
+        w["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one full-size launch (see profiles/)"
 
     def fwd():
         for x in parts:

@@ -221,7 +221,7 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
                                              const uint32_t score_flags, const int X, volatile const int* wi,
                                              const uint32_t tmem, const uint32_t sbase, volatile int* abort_flag,
                                              const CUtensorMap* tmO, float* __restrict__ Mout, float* __restrict__ Lout,
-                                             const int ph0) {
+                                             const int ph0, const bool single_item) {
   // wi: this warp's copy of the work item in shared memory (see WI_*), read where a value is used instead
   // of being carried in registers through the tile loop, whose 128 scores per thread leave no room;
   // ph0: key tiles this warpgroup has walked in the CTA's earlier work items (mbarrier phases go on
@@ -351,11 +351,11 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
             for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
           }
         }
+        const int qpos = wi[WI_Q0] + r + p.input_pos;
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
           float s = __uint_as_float(sr[q][t]) * p.scale;
           const int kv = kv0 + q * 32 + t;
-          const int qpos = wi[WI_Q0] + r + p.input_pos;
           const bool cap_first = score_flags & TYLO_SCORE_SOFTCAP_FIRST;
           if ((score_flags & TYLO_SCORE_SOFTCAP) && cap_first) s = softcap(s, p.cap, inv_cap);
           if (score_flags & TYLO_SCORE_ALIBI) s = fmaf(slope, (float)(qpos - kv), s);
@@ -528,22 +528,41 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     // and clips rows beyond Sq.  Row-by-row 16-byte stores straight from the registers would touch 32
     // lines per instruction and hold up every other shared- and global-memory instruction of the SM.
     // (q_lim is a multiple of 64 and a warp's first row of 32: a warp's rows are all live or all not.)
+    // A CTA with a single work item has nothing to hide the stores under, but its Q tile is free by now
+    // (the accumulator being complete means every Q K^T product has run; n > 0 means the tile was awaited):
+    // the warp's boxes go into its quarter of that tile, one buffer each, and no box waits for the one before.
     if (__shfl_sync(0xffffffffu, (int)live, 0)) {
-      const uint32_t buf = sbase + SM::kStage + (warp - 4) * 2048;
+      const bool wide = single_item && n > 0;
+      const uint32_t buf0 = wide ? sbase + SM::kQ + X * SM::kTile + wq * (SM::kTile / 4) : sbase + SM::kStage + (warp - 4) * 2048;
       const int row0 = wi[WI_Q0] + wq * 32, bh = wi[WI_B] * p.H + wi[WI_H];
-#pragma unroll
-      for (int q = 0; q < D / 32; ++q) {
-        if (lane == 0) bulk_wait_read();          // the box before this one has been read out of the buffer
-        __syncwarp();
+      auto stage = [&](int q, uint32_t buf) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           const uint32_t dst = buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(out[q][v].x), "r"(out[q][v].y),
                        "r"(out[q][v].z), "r"(out[q][v].w) : "memory");
         }
+      };
+      if (wide) {
+#pragma unroll
+        for (int q = 0; q < D / 32; ++q) stage(q, buf0 + q * 2048);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) { tma_store_3d(tmO, buf, q * 32, row0, bh); bulk_commit(); }
+        if (lane == 0) {
+#pragma unroll
+          for (int q = 0; q < D / 32; ++q) tma_store_3d(tmO, buf0 + q * 2048, q * 32, row0, bh);
+          bulk_commit();
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < D / 32; ++q) {
+          if (lane == 0) bulk_wait_read();          // the box before this one has been read out of the buffer
+          __syncwarp();
+          stage(q, buf0);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { tma_store_3d(tmO, buf0, q * 32, row0, bh); bulk_commit(); }
+        }
       }
     }
     if (live) {
@@ -792,7 +811,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int k = 0; k < n_local && ok; ++k) {
       volatile const int* wi = tab + k * IT_WORDS + X * WI_WORDS;
       if (tab[k * IT_WORDS + IT_NTOT] < 0) continue;
-      ok = softmax_tile<T, D, MASK, SCORE>(p, mask_flags, score_flags, X, wi, tmem, sbase, abort_flag, &tmO, Mout, Lout, ph);
+      ok = softmax_tile<T, D, MASK, SCORE>(p, mask_flags, score_flags, X, wi, tmem, sbase, abort_flag, &tmO, Mout, Lout, ph, paired == 0);
       ph += wi[WI_N];
     }
     if (lane == 0) bulk_wait_read();      // the last boxes have left the staging buffer
