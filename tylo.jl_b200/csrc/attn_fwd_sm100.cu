@@ -227,6 +227,14 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
   // ph0: key tiles this warpgroup has walked in the CTA's earlier work items (mbarrier phases go on
   // counting across items).
   using SM = FwdSmem<D>;
+  // Two forms of the tile loop.  Register-resident (no mods, at most a causal mask): the row's 128 scores
+  // stay in registers from the load to the probabilities.  Chunked (everything else): mods, mask and max run
+  // over 32 columns at a time in a rolled loop, the changed scores go back to tensor memory and a second
+  // rolled loop turns them into probabilities; the loop body is a quarter of the unrolled tile, which matters
+  // because the mod and mask code of a whole unrolled tile does not fit the instruction cache next to the other
+  // roles (config-4 mods: 0.336 ms register-resident, 0.279 ms chunked; the plain causal forward is 7 % slower
+  // chunked, since it reads every score twice for nothing).
+  constexpr bool kChunked = (MASK & ~(uint32_t)TYLO_MASK_CAUSAL) != 0 || SCORE != 0;
   auto bar = [&](int i) { return sbase + SM::kBars + 8 * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wq = warp & 3;                       // TMEM lane quarter this warp may touch
@@ -284,11 +292,6 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       pass_empty_tile();
       continue;
     }
-    uint32_t sr[4][32];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) tmem_ld32(ts + q * 32, sr[q]);
-    tc_wait_ld();
-
     // which tiles need the element-wise mask?
     bool partial = kv0 + BN > k_len_i;
     if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING | TYLO_MASK_PREFIX_LM)) partial = partial || (kv0 + BN - 1 > q_lo);
@@ -299,110 +302,26 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     const bool doc_elementwise = (mask_flags & TYLO_MASK_DOCUMENT) && !doc_uniform;
     const bool row_doc_ok = !(mask_flags & TYLO_MASK_DOCUMENT) || doc_elementwise || (__shfl_sync(0xffffffffu, ids[0], 0) == my_doc);
 
-    // score mods (compile-time selected), then the element-wise mask only on tiles that need it
-    // (a warp-uniform branch around the whole pass), then the row max over independent chains
-    bool mods_done = false;
-    if (modded && score_flags == TYLO_SCORE_SOFTCAP) {
-      // Soft cap alone: if every score of the warp's rows is small against the cap (the usual case),
-      // tanh is a branch-free odd polynomial on the FMA pipe for the whole tile.
-      float am[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-#pragma unroll
-        for (int t = 0; t < 32; t += 2)
-          am[q] = max3(am[q], fabsf(__uint_as_float(sr[q][t])), fabsf(__uint_as_float(sr[q][t + 1])));
-      }
-      if (__all_sync(0xffffffffu, fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * cap_k1 < 0.4f)) {
-        // cap*log2e*tanh(x), x = s*k1:  x (1 - x^2/3 + 2x^4/15 - 17x^6/315) = s * (a0 + u (a1 + u (a2 + u a3))), u = s^2
-        const uint64_t a0 = pack_f32x2(cap_a0, cap_a0), a1 = pack_f32x2(cap_a1, cap_a1), a2 = pack_f32x2(cap_a2, cap_a2),
-                       a3 = pack_f32x2(cap_a3, cap_a3);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-          for (int t = 0; t < 32; t += 2) {
-            const uint64_t s2 = pack_f32x2(__uint_as_float(sr[q][t]), __uint_as_float(sr[q][t + 1]));
-            const uint64_t u2 = mul_f32x2(s2, s2);
-            float y0, y1;
-            unpack_f32x2(mul_f32x2(s2, fma_f32x2(u2, fma_f32x2(u2, fma_f32x2(u2, a3, a2), a1), a0)), y0, y1);
-            sr[q][t] = __float_as_uint(y0); sr[q][t + 1] = __float_as_uint(y1);
-          }
-        }
-        mods_done = true;
-      }
-    }
-    if (modded && !mods_done) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        // BiasScore (mods.jl:219-237): this row's 32 table entries for the chunk, local row index, heads and
-        // batch broadcast by modulo; 16-byte loads when the row start is aligned, guarded scalars otherwise.
-        float bias_row[32];
-        if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) {
-          const int row_b = min(wi[WI_Q0] + r, p.Sq - 1);
-          const float* bp = p.bias + bias_index(p, wi[WI_B], wi[WI_H], row_b, 0);
-          const int kvq = kv0 + q * 32;
-          if ((p.Sk & 3) == 0 && kvq + 32 <= p.Sk) {
-#pragma unroll
-            for (int t = 0; t < 32; t += 4) {
-              const float4 v = __ldg(reinterpret_cast<const float4*>(bp + kvq + t));
-              bias_row[t] = v.x; bias_row[t + 1] = v.y; bias_row[t + 2] = v.z; bias_row[t + 3] = v.w;
-            }
-          } else {
-#pragma unroll
-            for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
-          }
-        }
-        const int qpos = wi[WI_Q0] + r + p.input_pos;
-#pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float s = __uint_as_float(sr[q][t]) * p.scale;
-          const int kv = kv0 + q * 32 + t;
-          const bool cap_first = score_flags & TYLO_SCORE_SOFTCAP_FIRST;
-          if ((score_flags & TYLO_SCORE_SOFTCAP) && cap_first) s = softcap(s, p.cap, inv_cap);
-          if (score_flags & TYLO_SCORE_ALIBI) s = fmaf(slope, (float)(qpos - kv), s);
-          if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) s += bias_row[t];
-          if ((score_flags & TYLO_SCORE_SOFTCAP) && !cap_first) s = softcap(s, p.cap, inv_cap);
-          sr[q][t] = __float_as_uint(s * kLog2e);
-        }
-      }
-    }
+    // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
+    // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
+    // compare per element against the tile-relative start: key kv0 + c is kept iff row_lo <= kv0 + c <= row_hi,
+    // (unsigned)(c - rel) <= span with rel = row_lo - kv0; a row that keeps nothing gets a start no column
+    // can reach.  OrMask in disjunctive normal form (mods.jl:164-167): every conjunction of affine terms is
+    // one more interval, a key is kept if any of them holds it (document terms inside an OR run on the
+    // fp32-arithmetic kernels, see the dispatch).
+    int rels[1 + kMaxOrClauses]; unsigned spans[1 + kMaxOrClauses];
+    rels[0] = 0x40000000; spans[0] = 0u;
     if (partial) {
       const int qpos = wi[WI_Q0] + r + p.input_pos;
-  // Every mask term except an element-wise document comparison keeps ONE interval of keys per row:
-      // [row_lo, row_hi] (mods.jl:101-167 reduced to bounds).  Inside a tile the test is then one unsigned
-      // compare per element against the tile-relative start.
       int row_lo = 0, row_hi = wi[WI_KLEN] - 1;
       if (mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) row_hi = min(row_hi, qpos);
       if (mask_flags & TYLO_MASK_SLIDING) row_lo = max(row_lo, qpos - p.window);
       if (mask_flags & TYLO_MASK_PREFIX) row_hi = min(row_hi, p.prefix_len - 1);
       if (mask_flags & TYLO_MASK_PREFIX_LM) row_hi = min(row_hi, max(qpos, p.prefix_len - 1));
       const bool row_any = row_hi >= row_lo;
-      const unsigned row_span = row_any ? (unsigned)(row_hi - row_lo) : 0u;
-      // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
-      // runtime condition makes the compiler wrap every one of the 128 in a convergence barrier.
-      // key kv0 + c is kept iff row_lo <= kv0 + c <= row_hi: (unsigned)(c - rel) <= row_span with
-      // rel = row_lo - kv0; a row that keeps nothing gets a start no column can reach.
-      const int rel = (row_any && row_doc_ok) ? row_lo - kv0 : 0x40000000;
-      auto mask_pass = [&](auto with_doc) {
-        constexpr bool DOCS = decltype(with_doc)::value;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            bool keep = (unsigned)(q * 32 + t - rel) <= row_span;
-            if (DOCS) {
-              const int key_doc = __shfl_sync(0xffffffffu, ids[q], t);   // every lane takes part, masked or not
-              keep = keep && (key_doc == my_doc);
-            }
-            sr[q][t] = keep ? sr[q][t] : 0xff800000u;   // -inf
-          }
-        }
-      };
+      spans[0] = row_any ? (unsigned)(row_hi - row_lo) : 0u;
+      rels[0] = (row_any && row_doc_ok) ? row_lo - kv0 : 0x40000000;
       if (MASK == kRuntimeMods && p.n_or > 0) {
-        // OrMask in disjunctive normal form (mods.jl:164-167): every conjunction of affine terms is one
-        // interval of keys per row; a key is kept if any of them holds it (document terms inside an OR run
-        // on the fp32-arithmetic kernels, see the dispatch).
-        int rels[1 + kMaxOrClauses]; unsigned spans[1 + kMaxOrClauses];
-        rels[0] = rel; spans[0] = row_span;
 #pragma unroll
         for (int ci = 0; ci < kMaxOrClauses; ++ci) {
           rels[1 + ci] = 0x40000000; spans[1 + ci] = 0u;
@@ -416,30 +335,146 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
             if (hi >= lo) { rels[1 + ci] = lo - kv0; spans[1 + ci] = (unsigned)(hi - lo); }
           }
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            bool keep = false;
-#pragma unroll
-            for (int ci = 0; ci < 1 + kMaxOrClauses; ++ci) keep = keep || ((unsigned)(q * 32 + t - rels[ci]) <= spans[ci]);
-            sr[q][t] = keep ? sr[q][t] : 0xff800000u;   // -inf
-          }
-        }
-      } else if (doc_elementwise) mask_pass(std::true_type{}); else mask_pass(std::false_type{});
-    }
-    float mxq[4][2];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      mxq[q][0] = -INFINITY; mxq[q][1] = -INFINITY;
-#pragma unroll
-      for (int t = 0; t < 32; t += 4) {
-        mxq[q][0] = max3(mxq[q][0], __uint_as_float(sr[q][t]), __uint_as_float(sr[q][t + 1]));
-        mxq[q][1] = max3(mxq[q][1], __uint_as_float(sr[q][t + 2]), __uint_as_float(sr[q][t + 3]));
       }
     }
-    const float mx = fmaxf(fmaxf(max3(mxq[0][0], mxq[0][1], mxq[1][0]), max3(mxq[1][1], mxq[2][0], mxq[2][1])),
-                           fmaxf(mxq[3][0], mxq[3][1]));
+
+    // ---- the steps of one chunk: 32 key columns (chunk q of the tile) of this thread's row ----
+    // score mods (compile-time selected)
+    auto apply_mods = [&](uint32_t (&v)[32], const int q) {
+      if (score_flags == TYLO_SCORE_SOFTCAP) {
+        // Soft cap alone: if every score of the warp's rows is small against the cap (the usual case),
+        // tanh is a branch-free odd polynomial on the FMA pipe for the whole chunk.
+        float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+        for (int t = 0; t < 32; t += 4) {
+          am0 = max3(am0, fabsf(__uint_as_float(v[t])), fabsf(__uint_as_float(v[t + 1])));
+          am1 = max3(am1, fabsf(__uint_as_float(v[t + 2])), fabsf(__uint_as_float(v[t + 3])));
+        }
+        if (__all_sync(0xffffffffu, fmaxf(am0, am1) * cap_k1 < 0.4f)) {
+          // cap*log2e*tanh(x), x = s*k1:  x (1 - x^2/3 + 2x^4/15 - 17x^6/315) = s * (a0 + u (a1 + u (a2 + u a3))), u = s^2
+          const uint64_t a0 = pack_f32x2(cap_a0, cap_a0), a1 = pack_f32x2(cap_a1, cap_a1), a2 = pack_f32x2(cap_a2, cap_a2),
+                         a3 = pack_f32x2(cap_a3, cap_a3);
+#pragma unroll
+          for (int t = 0; t < 32; t += 2) {
+            const uint64_t s2 = pack_f32x2(__uint_as_float(v[t]), __uint_as_float(v[t + 1]));
+            const uint64_t u2 = mul_f32x2(s2, s2);
+            float y0, y1;
+            unpack_f32x2(mul_f32x2(s2, fma_f32x2(u2, fma_f32x2(u2, fma_f32x2(u2, a3, a2), a1), a0)), y0, y1);
+            v[t] = __float_as_uint(y0); v[t + 1] = __float_as_uint(y1);
+          }
+          return;
+        }
+      }
+      // BiasScore (mods.jl:219-237): this row's 32 table entries for the chunk, local row index, heads and
+      // batch broadcast by modulo; 16-byte loads when the row start is aligned, guarded scalars otherwise.
+      float bias_row[32];
+      const int kvq = kv0 + q * 32;
+      if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) {
+        const int row_b = min(wi[WI_Q0] + r, p.Sq - 1);
+        const float* bp = p.bias + bias_index(p, wi[WI_B], wi[WI_H], row_b, 0);
+        if ((p.Sk & 3) == 0 && kvq + 32 <= p.Sk) {
+#pragma unroll
+          for (int t = 0; t < 32; t += 4) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(bp + kvq + t));
+            bias_row[t] = f.x; bias_row[t + 1] = f.y; bias_row[t + 2] = f.z; bias_row[t + 3] = f.w;
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
+        }
+      }
+      const int qpos = wi[WI_Q0] + r + p.input_pos;
+      const bool cap_first = score_flags & TYLO_SCORE_SOFTCAP_FIRST;
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        float s = __uint_as_float(v[t]) * p.scale;
+        if ((score_flags & TYLO_SCORE_SOFTCAP) && cap_first) s = softcap(s, p.cap, inv_cap);
+        if (score_flags & TYLO_SCORE_ALIBI) s = fmaf(slope, (float)(qpos - (kvq + t)), s);
+        if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) s += bias_row[t];
+        if ((score_flags & TYLO_SCORE_SOFTCAP) && !cap_first) s = softcap(s, p.cap, inv_cap);
+        v[t] = __float_as_uint(s * kLog2e);
+      }
+    };
+    // element-wise mask (only on tiles that need it: a warp-uniform branch around the whole pass)
+    auto apply_mask = [&](uint32_t (&v)[32], const int q) {
+      const int sh = q * 32;
+      if (MASK == kRuntimeMods && p.n_or > 0) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          bool keep = false;
+#pragma unroll
+          for (int ci = 0; ci < 1 + kMaxOrClauses; ++ci) keep = keep || ((unsigned)(sh + t - rels[ci]) <= spans[ci]);
+          v[t] = keep ? v[t] : 0xff800000u;   // -inf
+        }
+      } else if (doc_elementwise) {
+        // The document-id shuffles live in their own copy of the loop: a shuffle under a per-element
+        // runtime condition makes the compiler wrap every one of them in a convergence barrier.
+        const int idq = q == 0 ? ids[0] : (q == 1 ? ids[1] : (q == 2 ? ids[2] : ids[3]));
+        const int relq = rels[0] - sh;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const int key_doc = __shfl_sync(0xffffffffu, idq, t);   // every lane takes part, masked or not
+          v[t] = ((unsigned)(t - relq) <= spans[0] && key_doc == my_doc) ? v[t] : 0xff800000u;
+        }
+      } else {
+        const int relq = rels[0] - sh;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = ((unsigned)(t - relq) <= spans[0]) ? v[t] : 0xff800000u;
+      }
+    };
+    // row max over two independent chains
+    auto chunk_max = [&](const uint32_t (&v)[32]) -> float {
+      float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < 32; t += 4) {
+        m0 = max3(m0, __uint_as_float(v[t]), __uint_as_float(v[t + 1]));
+        m1 = max3(m1, __uint_as_float(v[t + 2]), __uint_as_float(v[t + 3]));
+      }
+      return fmaxf(m0, m1);
+    };
+
+    float mx;
+    uint32_t sr[4][32];     // the whole tile's scores of this row (register-resident form only)
+    if constexpr (!kChunked) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld32(ts + q * 32, sr[q]);
+      tc_wait_ld();
+      if (modded) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) apply_mods(sr[q], q);
+      }
+      if (partial) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) apply_mask(sr[q], q);
+      }
+      mx = fmaxf(fmaxf(chunk_max(sr[0]), chunk_max(sr[1])), fmaxf(chunk_max(sr[2]), chunk_max(sr[3])));
+    } else {
+      // Pass 1 of the chunked form: mods, mask and max chunk by chunk, the changed scores written back to
+      // tensor memory; the next chunk's load is in flight while the current one is worked on.
+      uint32_t a[32], b[32];
+      float mxa = -INFINITY, mxb = -INFINITY;
+      const bool changed = modded || partial;
+      tmem_ld32(ts, a);
+      tc_wait_ld_for(a);
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const int qa = 2 * h, qb = 2 * h + 1;
+        tmem_ld32(ts + qb * 32, b);
+        if (modded) apply_mods(a, qa);
+        if (partial) apply_mask(a, qa);
+        mxa = fmaxf(mxa, chunk_max(a));
+        if (changed) tmem_st32(ts + qa * 32, a);
+        tc_wait_ld_for(b);
+        if (h == 0) tmem_ld32(ts + 64, a);
+        if (modded) apply_mods(b, qb);
+        if (partial) apply_mask(b, qb);
+        mxb = fmaxf(mxb, chunk_max(b));
+        if (changed) tmem_st32(ts + qb * 32, b);
+        if (h == 0) tc_wait_ld_for(a);
+      }
+      mx = fmaxf(mxa, mxb);
+      if (changed) tc_wait_st();      // pass 2 reads them back
+    }
     m_true = fmaxf(m_true, mx);
     if (__all_sync(0xffffffffu, mx == -INFINITY)) {
       // every pair of this warp's 32 rows is masked in this tile (e.g. keys of another document):
@@ -464,31 +499,52 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     }
     if (need) m_ref = mx;
     const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
-    float lsq[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
     // Two scores per instruction on the FMA pipe: fma.rn.f32x2 for the exponent arguments and
     // add.rn.f32x2 for the running row sums (register pairs, sm_100 packed fp32).
     const uint64_t c2 = pack_f32x2(c, c), mc2 = pack_f32x2(-mc, -mc);
-    uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    // P of one chunk: 32 probabilities as 16 columns of packed pairs; returns their sum
+    auto exp_chunk = [&](const uint32_t (&v)[32], const int q) -> float {
       uint32_t pk[16];
+      uint64_t ls2 = 0ull;
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
         float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[q][2 * t]), __uint_as_float(sr[q][2 * t + 1])), c2, mc2), x0, x1);
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1])), c2, mc2), x0, x1);
         const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        ls2[q] = add_f32x2(ls2[q], pack_f32x2(p0, p1));
+        ls2 = add_f32x2(ls2, pack_f32x2(p0, p1));
         pk[t] = pack_pair<T>(p0, p1);
       }
-      unpack_f32x2(ls2[q], lsq[q][0], lsq[q][1]);
-      // 16 columns of packed pairs = 32 probabilities
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
           ::"r"(ts + q * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]),
             "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
             "r"(pk[15]) : "memory");
+      float s0, s1;
+      unpack_f32x2(ls2, s0, s1);
+      return s0 + s1;
+    };
+    if constexpr (!kChunked) {
+      const float s0 = exp_chunk(sr[0], 0), s1 = exp_chunk(sr[1], 1), s2 = exp_chunk(sr[2], 2), s3 = exp_chunk(sr[3], 3);
+      l += (s0 + s1) + (s2 + s3);
+    } else {
+      // Pass 2: P chunk q lands on the columns of score chunk q / 2, which has been read by then.
+      uint32_t a[32], b[32];
+      float lt = 0.f;
+      tmem_ld32(ts, a);
+      tc_wait_ld_for(a);
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const int qa = 2 * h, qb = 2 * h + 1;
+        tmem_ld32(ts + qb * 32, b);
+        const float sa = exp_chunk(a, qa);
+        tc_wait_ld_for(b);
+        if (h == 0) tmem_ld32(ts + 64, a);
+        const float sb = exp_chunk(b, qb);
+        if (h == 0) tc_wait_ld_for(a);
+        lt += sa + sb;
+      }
+      l += lt;
     }
-    l += ((lsq[0][0] + lsq[0][1]) + (lsq[1][0] + lsq[1][1])) + ((lsq[2][0] + lsq[2][1]) + (lsq[3][0] + lsq[3][1]));
     tc_wait_st();
     tc_fence_before();
     mbar_arrive(bar(SM::P_FULL + X));
