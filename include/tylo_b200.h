@@ -42,7 +42,15 @@ typedef enum {
   TYLO_ERR_WORKSPACE = 7         /* caller-provided workspace is too small */
 } tylo_status;
 
-typedef enum { TYLO_F32 = 0, TYLO_BF16 = 1, TYLO_F16 = 2 } tylo_dtype;
+typedef enum {
+  TYLO_F32 = 0, TYLO_BF16 = 1, TYLO_F16 = 2,
+  /* Float32 storage with the matrix products on the tensor cores, operands read as TF32 (sign, exponent,
+   * 10 mantissa bits; fp32 accumulation and fp32 softmax) — the reference's default for Float32
+   * (`tensorcore = TFloat32`, src/utils.jl:43-44).  Accepted by the attention and flex-attention FORWARD
+   * entry points for head dims 32 and 64; other head dims, block lists and OR-ed document terms are computed
+   * in true fp32 there.  Every other entry point rejects it: pass TYLO_F32. */
+  TYLO_F32_TF32 = 3
+} tylo_dtype;
 
 typedef void* tylo_stream_t; /* cudaStream_t */
 

@@ -36,8 +36,9 @@ if not _LIB_PATH.exists():
         "(libtylo_b200 has no CPU or pure-PyTorch fallback)")
 _lib = ctypes.CDLL(str(_LIB_PATH))
 
-F32, BF16, F16 = 0, 1, 2
+F32, BF16, F16, F32_TF32 = 0, 1, 2, 3
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+TFloat32 = "TFloat32"      # value of the `tensorcore` keyword that asks for TF32 products on Float32 storage
 
 MASK_CAUSAL, MASK_SLIDING, MASK_DOCUMENT, MASK_PREFIX, MASK_PREFIX_LM = 1, 2, 4, 8, 16
 SCORE_ALIBI, SCORE_SOFTCAP, SCORE_SOFTCAP_FIRST, SCORE_BIAS = 1, 2, 4, 8
@@ -157,6 +158,22 @@ def _dtype(t: torch.Tensor) -> int:
         return _DTYPES[t.dtype]
     except KeyError:
         raise TypeError(f"unsupported element type {t.dtype}") from None
+
+
+def _fwd_dtype(t: torch.Tensor, tensorcore) -> int:
+    """Element-type code of a forward attention call.  `tensorcore` mirrors the reference's keyword
+    (utils.jl:43-44: Float32 storage defaults to TFloat32 operands there): None computes Float32 in true fp32;
+    TFloat32 / "tf32" reads the operands of both matrix products as TF32 on the tensor cores (Float32 storage
+    only; 16-bit storage always runs in its own type, as in the reference)."""
+    code = _dtype(t)
+    if tensorcore is None:
+        return code
+    name = tensorcore if isinstance(tensorcore, str) else getattr(tensorcore, "__name__", str(tensorcore))
+    if name.lower() in ("tfloat32", "tf32"):
+        return F32_TF32 if code == F32 else code
+    if name.lower() in ("float32", "fp32", "f32", "bfloat16", "bf16", "float16", "f16", "fp16"):
+        return code
+    raise ValueError(f"tensorcore={tensorcore!r}: expected None or TFloat32")
 
 
 def _dense(*ts):
@@ -697,16 +714,18 @@ def allocate_scratchspace_grad_attention(Q, K, V, O) -> AttnScratch:
     return AttnScratch(None, torch.empty(B, H, Sq, dtype=torch.float32, device=Q.device), ws)
 
 
-def attention_(O, Q, K, V, *, causal=False, input_pos=0, k_lengths=None, q_lengths=None, checkpoints=None):
-    """attention!(O, Q, K, V; ...) (attention.jl:219-262).  Returns None."""
+def attention_(O, Q, K, V, *, causal=False, input_pos=0, k_lengths=None, q_lengths=None, checkpoints=None,
+               tensorcore=None):
+    """attention!(O, Q, K, V; ...) (attention.jl:219-262).  Returns None.  `tensorcore=TFloat32` on Float32
+    arrays: products on the tensor cores with TF32 operands (head dims 32 and 64); default true fp32."""
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
     _dense(pO, pQ, pK, pV, k_lengths, q_lengths)
     M = None if checkpoints is None else checkpoints.M
     L = None if checkpoints is None else checkpoints.L
     _check(_lib.tylo_b200_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), _p(k_lengths), _p(q_lengths),
-                                        Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos), int(bool(causal)), _dtype(pQ),
-                                        _stream()))
+                                        Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos), int(bool(causal)),
+                                        _fwd_dtype(pQ, tensorcore), _stream()))
 
 
 def attention(Q, K, V, **kw):
@@ -764,7 +783,7 @@ def _check_block_mask(bm: BlockMask, Sq: int) -> None:
 
 
 def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=None, block_sparse=True,
-                    input_pos=0, qk_scale=None, checkpoints=None):
+                    input_pos=0, qk_scale=None, checkpoints=None, tensorcore=None):
     """flex_attention!(O, Q, K, V; score_mod, mask_mod, ...) (flex.jl:312-383)."""
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
@@ -789,7 +808,7 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
     _check(_lib.tylo_b200_flex_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md),
                                              ctypes.byref(sd), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),
                                              0.0 if qk_scale is None else float(qk_scale), int(bool(block_sparse)),
-                                             _dtype(pQ), _stream()))
+                                             _fwd_dtype(pQ, tensorcore), _stream()))
 
 
 def flex_attention(Q, K, V, **kw):

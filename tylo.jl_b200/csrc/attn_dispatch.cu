@@ -22,6 +22,7 @@ static bool table_mods(const AttnParams& p) {
 int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                           const AttnParams& p, int32_t dtype, cudaStream_t st) {
   if (!fwd_needs_generic(p) && attn_fwd_sm100_supported(p, dtype)) return attn_fwd_sm100(O, Q, K, V, M, L, p, dtype, st);
+  if (dtype == TYLO_F32_TF32) dtype = TYLO_F32;      // no tensor-core form for this call: true fp32
   TYLO_DISPATCH_DTYPE(dtype, T, return attn_fwd_generic<T>(O, Q, K, V, M, L, p, st));
   return TYLO_OK;
 }

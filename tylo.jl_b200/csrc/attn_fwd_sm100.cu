@@ -52,9 +52,12 @@ enum { IT_A = 0, IT_B = WI_WORDS, IT_NTOT = 2 * WI_WORDS, IT_JLO, IT_AS, IT_AE, 
        IT_WORDS };
 constexpr int kMaxItems = 40;
 
-template <int D> struct FwdSmem {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
-  static constexpr int kTile = BM * D * 2;             // bytes of one Q / K / V tile
+// DB: bytes of one row of a Q / K / V tile (head dim x element size): 256 (16-bit D 128, TF32 D 64) or
+// 128 (16-bit D 64, TF32 D 32).  A row is one or two 128-byte swizzle atoms whatever the element type, so
+// the tile geometry, the TMA boxes and the descriptor arithmetic are written in bytes.
+template <int DB> struct FwdSmem {
+  static constexpr int kStages = (DB == 256) ? 2 : 4;
+  static constexpr int kTile = BM * DB;                // bytes of one Q / K / V tile
   static constexpr int kQ = 0;                          // two Q tiles
   static constexpr int kK = 2 * kTile;
   static constexpr int kV = kK + kStages * kTile;
@@ -75,6 +78,7 @@ template <int D> struct FwdSmem {
 template <typename T> struct MmaFmt;
 template <> struct MmaFmt<__nv_bfloat16> { static constexpr int v = 1; };
 template <> struct MmaFmt<__half> { static constexpr int v = 0; };
+template <> struct MmaFmt<float> { static constexpr int v = 2; };    // TF32: the low 13 mantissa bits are not read
 
 template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
@@ -226,7 +230,7 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
   // of being carried in registers through the tile loop, whose 128 scores per thread leave no room;
   // ph0: key tiles this warpgroup has walked in the CTA's earlier work items (mbarrier phases go on
   // counting across items).
-  using SM = FwdSmem<D>;
+  using SM = FwdSmem<D * (int)sizeof(T)>;
   // Two forms of the tile loop.  Register-resident (no mods, at most a causal mask): the row's 128 scores
   // stay in registers from the load to the probabilities.  Chunked (everything else): mods, mask and max run
   // over 32 columns at a time in a rolled loop, the changed scores go back to tensor memory and a second
@@ -282,7 +286,8 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       uint32_t z[32];
 #pragma unroll
       for (int t = 0; t < 32; ++t) z[t] = 0u;
-      tmem_st32(ts, z); tmem_st32(ts + 32, z);
+#pragma unroll
+      for (int cq = 0; cq < (sizeof(T) == 4 ? 4 : 2); ++cq) tmem_st32(ts + cq * 32, z);   // 128 packed pairs or 128 fp32
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(SM::P_FULL + X));
@@ -504,21 +509,42 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     const uint64_t c2 = pack_f32x2(c, c), mc2 = pack_f32x2(-mc, -mc);
     // P of one chunk: 32 probabilities as 16 columns of packed pairs; returns their sum
     auto exp_chunk = [&](const uint32_t (&v)[32], const int q) -> float {
-      uint32_t pk[16];
       uint64_t ls2 = 0ull;
+      auto st16 = [&](uint32_t col, const uint32_t (&pk)[16]) {
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(col), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]),
+              "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
+              "r"(pk[15]) : "memory");
+      };
+      if constexpr (sizeof(T) == 4) {
+        // TF32 operand: the probabilities stay 32-bit, in place of their scores, 16 columns per store
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1])), c2, mc2), x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        ls2 = add_f32x2(ls2, pack_f32x2(p0, p1));
-        pk[t] = pack_pair<T>(p0, p1);
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[hh * 16 + 2 * t]), __uint_as_float(v[hh * 16 + 2 * t + 1])), c2, mc2),
+                         x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            ls2 = add_f32x2(ls2, pack_f32x2(p0, p1));
+            pk[2 * t] = __float_as_uint(p0); pk[2 * t + 1] = __float_as_uint(p1);
+          }
+          st16(ts + q * 32 + hh * 16, pk);
+        }
+      } else {
+        uint32_t pk[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1])), c2, mc2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          ls2 = add_f32x2(ls2, pack_f32x2(p0, p1));
+          pk[t] = pack_pair<T>(p0, p1);
+        }
+        st16(ts + q * 16, pk);      // 16 columns of packed pairs = 32 probabilities
       }
-      asm volatile(
-          "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-          ::"r"(ts + q * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]),
-            "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
-            "r"(pk[15]) : "memory");
       float s0, s1;
       unpack_f32x2(ls2, s0, s1);
       return s0 + s1;
@@ -562,24 +588,32 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     const bool live = row < wi[WI_QLIM];
     // The whole accumulator row is read out and packed first, so that the MMA issuer can start the next
     // work item's P V products while this warpgroup stores.
-    uint4 out[D / 32][4];
+    // A box is 32 rows x 64 bytes: 32 columns of a 16-bit type, 16 columns of fp32.
+    constexpr int kBoxes = D * (int)sizeof(T) / 64, kBoxCols = 64 / (int)sizeof(T);
+    uint4 out[kBoxes][4];
 #pragma unroll
     for (int q = 0; q < D / 32; ++q) {
       uint32_t orr[32];
       if (n > 0) { tmem_ld32(to + q * 32, orr); tc_wait_ld(); }
-      uint32_t* ow = reinterpret_cast<uint32_t*>(out[q]);
+      if constexpr (sizeof(T) == 4) {
+        uint32_t* ow = reinterpret_cast<uint32_t*>(out[2 * q]);     // two boxes per 32 accumulator columns
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        const float a = (n > 0) ? __uint_as_float(orr[2 * t]) * inv : 0.f;
-        const float bb = (n > 0) ? __uint_as_float(orr[2 * t + 1]) * inv : 0.f;
-        ow[t] = pack_pair<T>(a, bb);
+        for (int t = 0; t < 32; ++t) ow[t] = (n > 0) ? __float_as_uint(__uint_as_float(orr[t]) * inv) : 0u;
+      } else {
+        uint32_t* ow = reinterpret_cast<uint32_t*>(out[q]);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const float a = (n > 0) ? __uint_as_float(orr[2 * t]) * inv : 0.f;
+          const float bb = (n > 0) ? __uint_as_float(orr[2 * t + 1]) * inv : 0.f;
+          ow[t] = pack_pair<T>(a, bb);
+        }
       }
     }
     if (wi[WI_RELEASE]) {
       tc_fence_before();
       mbar_arrive(bar(SM::O_FREE + X));
     }
-    // Output rows leave through shared memory: each warp stages 32 rows x 32 columns (2 KB, 64-byte swizzle,
+    // Output rows leave through shared memory: each warp stages boxes of 32 rows x 64 bytes (2 KB, 64-byte swizzle,
     // conflict-free 16-byte stores) and one lane hands the box to the TMA unit, which writes whole sectors
     // and clips rows beyond Sq.  Row-by-row 16-byte stores straight from the registers would touch 32
     // lines per instruction and hold up every other shared- and global-memory instruction of the SM.
@@ -601,23 +635,23 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       };
       if (wide) {
 #pragma unroll
-        for (int q = 0; q < D / 32; ++q) stage(q, buf0 + q * 2048);
+        for (int q = 0; q < kBoxes; ++q) stage(q, buf0 + q * 2048);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
 #pragma unroll
-          for (int q = 0; q < D / 32; ++q) tma_store_3d(tmO, buf0 + q * 2048, q * 32, row0, bh);
+          for (int q = 0; q < kBoxes; ++q) tma_store_3d(tmO, buf0 + q * 2048, q * kBoxCols, row0, bh);
           bulk_commit();
         }
       } else {
 #pragma unroll
-        for (int q = 0; q < D / 32; ++q) {
+        for (int q = 0; q < kBoxes; ++q) {
           if (lane == 0) bulk_wait_read();          // the box before this one has been read out of the buffer
           __syncwarp();
           stage(q, buf0);
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) { tma_store_3d(tmO, buf0, q * 32, row0, bh); bulk_commit(); }
+          if (lane == 0) { tma_store_3d(tmO, buf0, q * kBoxCols, row0, bh); bulk_commit(); }
         }
       }
     }
@@ -640,8 +674,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                       float* __restrict__ Mout,
                       float* __restrict__ Lout, const AttnParams p, const int paired) {
-  using SM = FwdSmem<D>;
+  using SM = FwdSmem<D * (int)sizeof(T)>;
   constexpr int ST = SM::kStages;
+  constexpr int DB = D * (int)sizeof(T);          // bytes of a tile row
+  constexpr int kAtom = 128 / (int)sizeof(T);      // elements of one 128-byte swizzle atom (one TMA box)
+  constexpr bool kTf32 = sizeof(T) == 4;           // fp32 storage, operands read as TF32
+  constexpr int kKeysPerMma = 32 / (int)sizeof(T); // K extent of one tcgen05.mma: 32 bytes
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_addr(smem);
@@ -733,15 +771,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (!ok) return;
             mbar_expect_tx(bar(SM::K_FULL + st), SM::kTile);
 #pragma unroll
-            for (int cc = 0; cc < D / 64; ++cc)
-              tma_load_3d(sbase + SM::kK + st * SM::kTile + cc * (BN * 128), &tmK, bar(SM::K_FULL + st), cc * 64, row, kvh);
+            for (int cc = 0; cc < DB / 128; ++cc)
+              tma_load_3d(sbase + SM::kK + st * SM::kTile + cc * (BN * 128), &tmK, bar(SM::K_FULL + st), cc * kAtom, row, kvh);
             k_loaded = g + 1;
             if (g >= ST) ok = mbar_wait(bar(SM::V_EMPTY + st), ((g / ST) - 1) & 1, abort_flag, &g_attn_fwd_status, 102);
             if (!ok) return;
             mbar_expect_tx(bar(SM::V_FULL + st), SM::kTile);
 #pragma unroll
-            for (int cc = 0; cc < D / 64; ++cc)
-              tma_load_3d(sbase + SM::kV + st * SM::kTile + cc * (BN * 128), &tmV, bar(SM::V_FULL + st), cc * 64, row, kvh);
+            for (int cc = 0; cc < DB / 128; ++cc)
+              tma_load_3d(sbase + SM::kV + st * SM::kTile + cc * (BN * 128), &tmV, bar(SM::V_FULL + st), cc * kAtom, row, kvh);
             v_loaded = g + 1;
             ++g;
           };
@@ -757,8 +795,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           for (int X = 0; X < 2; ++X) {
             mbar_expect_tx(bar(SM::Q_FULL + X), SM::kTile);
 #pragma unroll
-            for (int cc = 0; cc < D / 64; ++cc)
-              tma_load_3d(sbase + SM::kQ + X * SM::kTile + cc * (BM * 128), &tmQ, bar(SM::Q_FULL + X), cc * 64,
+            for (int cc = 0; cc < DB / 128; ++cc)
+              tma_load_3d(sbase + SM::kQ + X * SM::kTile + cc * (BM * 128), &tmQ, bar(SM::Q_FULL + X), cc * kAtom,
                           e[IT_Q0] + X * plan.q_step, e[IT_BATCH] * p.H + e[IT_HEAD] + X * plan.h_step);
           }
           for (int j = 1; j < n_tot && ok; ++j) load_kv(j);
@@ -774,7 +812,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // halves once and add a pre-shifted byte offset per MMA, so that the single issuing thread
         // spends a couple of integer instructions per tcgen05.mma instead of a dependent chain.
         const uint64_t dk_hi = smem_desc_sw128(0, 16, 1024);              // K-major Q / K operands
-        const uint64_t dv_hi = smem_desc_sw128(0, BN * 128, 1024);        // MN-major V operand
+        // MN-major V operand: atoms of 8 rows x 128 bytes (16-bit) or 4 rows x 128 bytes in 32-byte units (TF32)
+        const uint64_t dv_hi = kTf32 ? smem_desc_sw128_base32(0, BN * 128, 512) : smem_desc_sw128(0, BN * 128, 1024);
         auto desc_at = [](uint64_t hi, uint32_t saddr) { return hi | (uint64_t)((saddr & 0x3ffff) >> 4); };
         bool ok = true;
         int ni = 0, g0 = 0;      // non-empty items and K/V tiles of the items before this one
@@ -790,19 +829,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint64_t qd = desc_at(dk_hi, sbase + SM::kQ + X * SM::kTile);
             const uint64_t kd = desc_at(dk_hi, sbase + SM::kK + ((g0 + j) % ST) * SM::kTile);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
+            for (int kk = 0; kk < DB / 32; ++kk) {
               const uint32_t off = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4;   // compile-time constant
-              mma_ss(d, qd + off, kd + off, idesc_qk, kk > 0);
+              mma_ss<kTf32>(d, qd + off, kd + off, idesc_qk, kk > 0);
             }
             tc_commit(bar(SM::S_FULL + X));
           };
           auto issue_pv = [&](int X, int j) {
-            const uint32_t pa = tmem + X * 128;              // P: 64 columns of packed pairs
+            const uint32_t pa = tmem + X * 128;              // P: 64 columns of packed pairs (16-bit) or 128 of fp32 (TF32)
             const uint64_t vd = desc_at(dv_hi, sbase + SM::kV + ((g0 + j) % ST) * SM::kTile);
             const bool first = (j == ts[X]);
 #pragma unroll
-            for (int kk = 0; kk < BN / 16; ++kk)
-              mma_ts(tmem + 256 + X * 128, pa + kk * 8, vd + (uint32_t)((kk * 2048) >> 4), idesc_pv, !first || (kk > 0));
+            for (int kk = 0; kk < BN / kKeysPerMma; ++kk)     // 8 columns of P and kKeysPerMma rows of V per step
+              mma_ts<kTf32>(tmem + 256 + X * 128, pa + kk * 8, vd + (uint32_t)((kk * kKeysPerMma * 128) >> 4), idesc_pv,
+                            !first || (kk > 0));
             tc_commit(bar(SM::O_READY + X));
           };
           ok = mbar_wait(bar(SM::Q_FULL + 0), ni & 1, abort_flag, &g_attn_fwd_status, 201);
@@ -904,39 +944,42 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// 3-D view (D, S, heads*batch) of a dense (D,S,H,B) array; box = 64 x 128 x 1, 128-byte swizzle.
-// Output view for the epilogue's stores: box = 32 columns x 32 rows, 64-byte swizzle.
-static int32_t make_tmap_out(CUtensorMap* map, const void* base, int D, int S, int BH) {
+// 3-D view (D, S, heads*batch) of a dense (D,S,H,B) array of 2- or 4-byte elements; box = one 128-byte swizzle
+// atom x 128 rows x 1.  V with 4-byte elements is swizzled in 32-byte units (see smem_desc_sw128_base32).
+// Output view for the epilogue's stores: box = 64 bytes x 32 rows, 64-byte swizzle.
+static int32_t make_tmap_out(CUtensorMap* map, const void* base, int D, int S, int BH, int eb) {
   auto fn = encode_fn();
   TYLO_REQUIRE(fn, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
-  cuuint32_t box[3] = {32, 32, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)D * eb, (cuuint64_t)S * D * eb};
+  cuuint32_t box[3] = {(cuuint32_t)(64 / eb), 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map, eb == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TYLO_REQUIRE(r == CUDA_SUCCESS, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
   return TYLO_OK;
 }
 
-static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int BH) {
+static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int BH, int eb, bool mn_major = false) {
   auto fn = encode_fn();
   TYLO_REQUIRE(fn, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)BN, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)D * eb, (cuuint64_t)S * D * eb};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / eb), (cuuint32_t)BN, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map, eb == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  (eb == 4 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TYLO_REQUIRE(r == CUDA_SUCCESS, TYLO_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return TYLO_OK;
 }
 
 bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype) {
-  if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
-  if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
+  if (dtype != TYLO_BF16 && dtype != TYLO_F16 && dtype != TYLO_F32_TF32) return false;
+  if (p.Dk != p.Dv) return false;
+  if (dtype == TYLO_F32_TF32 ? (p.Dk != 32 && p.Dk != 64) : (p.Dk != 64 && p.Dk != 128)) return false;
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2) return false;
   return true;
 }
@@ -945,7 +988,7 @@ template <typename T, int D, uint32_t MASK, uint32_t SCORE>
 static int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, float* M,
                           float* L, const AttnParams& p, cudaStream_t st) {
   auto kern = attn_fwd_sm100_kernel<T, D, MASK, SCORE>;
-  TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<D>::kDynamic));
+  TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<D * (int)sizeof(T)>::kDynamic));
   // One work item per CTA while the items fit the SMs in one go, and whenever the items' costs cannot be told
   // in advance (windows, document masks, ragged lengths: the hardware's own CTA scheduling balances those
   // best — measured on the window + document configuration: 0.337 ms against 0.346 ms).  Otherwise one CTA per
@@ -969,7 +1012,7 @@ static int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CU
     const long long need = (n_slots + per_cta - 1) / per_cta;
     if (grid < need) grid = need;
   }
-  kern<<<(unsigned)grid, kFwdThreads, FwdSmem<D>::kDynamic, st>>>(mq, mk, mv, mo, M, L, p, paired);
+  kern<<<(unsigned)grid, kFwdThreads, FwdSmem<D * (int)sizeof(T)>::kDynamic, st>>>(mq, mk, mv, mo, M, L, p, paired);
   return check_launch("attn_fwd_sm100");
 }
 
@@ -978,6 +1021,12 @@ static int32_t dispatch_mods(const CUtensorMap& mq, const CUtensorMap& mk, const
                              float* L, const AttnParams& p, cudaStream_t st) {
   constexpr uint32_t C = TYLO_MASK_CAUSAL, W = TYLO_MASK_SLIDING, DOC = TYLO_MASK_DOCUMENT;
   const uint32_t m = p.mask_flags, s = p.score_flags;
+  if constexpr (sizeof(T) == 4) {
+    // TF32: the plain and the causal forward have their own variants, every mod goes through the run-time one
+    if (p.n_or == 0 && s == 0 && m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (p.n_or == 0 && s == 0 && m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, mo, M, L, p, st);
+    return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
+  } else {
   // OR-ed clauses and bias tables are handled by the variant that reads its flags at run time
   if (p.n_or > 0 || (s & TYLO_SCORE_BIAS)) return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
   if (s == 0) {
@@ -991,15 +1040,21 @@ static int32_t dispatch_mods(const CUtensorMap& mq, const CUtensorMap& mk, const
   if (s == TYLO_SCORE_SOFTCAP && m == C) return launch_fwd<T, D, C, TYLO_SCORE_SOFTCAP>(mq, mk, mv, mo, M, L, p, st);
   if (s == TYLO_SCORE_ALIBI && m == C) return launch_fwd<T, D, C, TYLO_SCORE_ALIBI>(mq, mk, mv, mo, M, L, p, st);
   return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
+  }
 }
 
 int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, float* M, float* L, const AttnParams& p,
                        int32_t dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
-  if (int32_t rc = make_tmap_out(&mo, O, p.Dv, p.Sq, p.H * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mq, Q, p.Dk, p.Sq, p.H * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mk, K, p.Dk, p.Sk, p.Hkv * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mv, V, p.Dv, p.Sk, p.Hkv * p.B)) return rc;
+  const int eb = dtype == TYLO_F32_TF32 ? 4 : 2;
+  if (int32_t rc = make_tmap_out(&mo, O, p.Dv, p.Sq, p.H * p.B, eb)) return rc;
+  if (int32_t rc = make_tmap(&mq, Q, p.Dk, p.Sq, p.H * p.B, eb)) return rc;
+  if (int32_t rc = make_tmap(&mk, K, p.Dk, p.Sk, p.Hkv * p.B, eb)) return rc;
+  if (int32_t rc = make_tmap(&mv, V, p.Dv, p.Sk, p.Hkv * p.B, eb, true)) return rc;   // V is the MN-major operand of P V
+  if (dtype == TYLO_F32_TF32) {
+    if (p.Dk == 64) return dispatch_mods<float, 64>(mq, mk, mv, mo, M, L, p, st);
+    return dispatch_mods<float, 32>(mq, mk, mv, mo, M, L, p, st);
+  }
   if (dtype == TYLO_BF16) {
     if (p.Dk == 128) return dispatch_mods<__nv_bfloat16, 128>(mq, mk, mv, mo, M, L, p, st);
     return dispatch_mods<__nv_bfloat16, 64>(mq, mk, mv, mo, M, L, p, st);

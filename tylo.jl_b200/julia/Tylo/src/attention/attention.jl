@@ -19,8 +19,9 @@ end
 
 Fused multi-head attention with GQA.  `Q (Dk,Sq,H,B)`, `K (Dk,Sk,Hkv,B)`, `V (Dv,Sk,Hkv,B)`,
 `O (Dv,Sq,H,B)`; scale `1/√Dk`.  `checkpoints = allocate_checkpoints(attention!, Q, K, V)` saves the
-softmax statistics for `∇attention!`.  `tensorcore`, `TILE_M`, `TILE_N` are accepted for source
-compatibility and ignored (tile shapes are fixed per kernel; Float32 is computed in true fp32).
+softmax statistics for `∇attention!`.  `TILE_M`, `TILE_N` are accepted for source compatibility and ignored
+(tile shapes are fixed per kernel).  `Float32` arrays are computed in true fp32 unless `tensorcore = TFloat32`
+asks for TF32 operands on the tensor cores (head dims 32 and 64).
 Returns `nothing`.
 """
 function attention!(O, Q, K, V; causal = false, input_pos = 0, k_lengths = nothing, q_lengths = nothing,
@@ -35,7 +36,7 @@ function attention!(O, Q, K, V; causal = false, input_pos = 0, k_lengths = nothi
         (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
          Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Ptr{Cvoid}),
         devptr(pO), devptr(pQ), devptr(pK), devptr(pV), devptr(M), devptr(L), devptr(k_lengths), devptr(q_lengths),
-        Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), Int32(causal), tylo_dtype(eltype(pQ)), current_stream()))
+        Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), Int32(causal), fwd_dtype(eltype(pQ), tensorcore), current_stream()))
     return
 end
 

@@ -11,6 +11,8 @@ a fully masked query gives `O = 0`, `M = -Inf`, `L = 0`).  Supported mods: `Caus
 else throws `ArgumentError`.  With `block_mask`
 (a `BlockMask` from `build_block_mask`) the forward walks the host-built block list instead of the
 analytic block range; `TILE_M` / `TILE_N` are the edges the mask was built with (multiples of 32).
+`tensorcore = TFloat32` on `Float32` arrays: TF32 operands on the tensor cores (head dims 32 and 64; block lists
+always run in true fp32).
 """
 function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMask(), block_mask = nothing,
                          block_sparse = true, input_pos = 0, qk_scale = nothing, tensorcore = nothing,
@@ -45,7 +47,7 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
              Int32, Int32, Int32, Int32, Int32, Int32, Int32, Int32, Float32, Int32, Int32, Ptr{Cvoid}),
             devptr(pO), devptr(pQ), devptr(pK), devptr(pV), devptr(M), devptr(L), md, sd,
             Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), qk_scale === nothing ? 0.0f0 : Float32(qk_scale),
-            Int32(block_sparse), tylo_dtype(eltype(pQ)), current_stream()))
+            Int32(block_sparse), fwd_dtype(eltype(pQ), tensorcore), current_stream()))
     end
     return
 end

@@ -9,6 +9,21 @@ tylo_dtype(::Type{BFloat16}) = Int32(1)
 tylo_dtype(::Type{Float16}) = Int32(2)
 tylo_dtype(T::Type) = throw(ArgumentError("libtylo_b200 has no kernels for element type $T"))
 
+"""
+    TFloat32
+
+Value of the `tensorcore` keyword of `attention!` / `flex_attention!` that asks for both matrix products on the
+tensor cores with TF32 operands for `Float32` arrays (the reference's default for `Float32`, utils.jl:43-44).
+The default here, `tensorcore = nothing`, computes `Float32` in true fp32.  Forward only, head dims 32 and 64.
+"""
+struct TFloat32 end
+export TFloat32
+
+"Element-type code of a forward attention call: `Float32` arrays with `tensorcore = TFloat32` run as TF32."
+fwd_dtype(T::Type, tensorcore) =
+    (T === Float32 && tensorcore !== nothing && nameof(tensorcore) === :TFloat32) ? Int32(3) : tylo_dtype(T)
+fwd_dtype(T::Type, ::Nothing) = tylo_dtype(T)
+
 # ---- the three version-dependent spellings -------------------------------------------------
 """
     devptr(a)
