@@ -210,10 +210,10 @@ def make_prefill(t, torch, seed, bwd=False, rank=0, world=1, sharded=False):
     w = dict(name=name, unit="TFLOP/s", bound="tensor", scale=1e-12)
     if not bwd and not sharded and B == 4:
         # DRAM bytes of one launch of the forward kernel on this very workload (batch 4, one launch per step):
-        # dram__bytes_read.sum 201,601,280 + dram__bytes_write.sum 104,224,768 from a one-launch, three-metric
+        # dram__bytes_read.sum 201,710,080 + dram__bytes_write.sum 104,483,584 from a one-launch, three-metric
         # ncu capture; the algorithmic bytes are 339.7 MB (Q, O 134.2 MB each, K + V 67.1 MB, statistics 4.2 MB),
         # the difference being output still in L2 when the kernel ends.
-        w["traffic"] = 305826048
+        w["traffic"] = 306193664
         w["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one full-size launch (see profiles/)"
 
     def fwd():
