@@ -14,7 +14,7 @@ static bool or_with_documents(const AttnParams& p) {
   for (int i = 0; i < p.n_or; ++i) doc = doc || (p.or_clause[i].flags & TYLO_MASK_DOCUMENT) != 0;
   return doc;
 }
-static bool fwd_needs_generic(const AttnParams& p) { return p.bm_count != nullptr || or_with_documents(p); }
+static bool fwd_needs_generic(const AttnParams& p) { return or_with_documents(p); }
 static bool table_mods(const AttnParams& p) {
   return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr || p.n_or > 0;
 }

@@ -23,6 +23,13 @@
 //                rescales O in TMEM only when the row max grew by more than 2^8 (lazy rescaling),
 //                and writes the final O through shared memory with TMA stores, M and L directly.
 //
+//                With score mods or a non-causal mask the tile is walked 32 columns at a time in rolled
+//                loops (see softmax_tile); the plain and the causal forward keep the row in registers.
+//
+// Element types: bf16 / f16 (kind::f16), and Float32 storage with the operands read as TF32 (kind::tf32,
+// head dims 32 and 64): the tile geometry is in bytes, P stays 32-bit in place of S, and V is loaded in the
+// 128-byte swizzle with 32-byte atoms, the only layout an MN-major TF32 operand may have.
+//
 // TMEM columns: [0,128) S_A/P_A, [128,256) S_B/P_B, [256,256+D) O_A, [384,384+D) O_B.
 // No multicast, no clusters.  Every mbarrier wait is bounded; a time-out sets a status word and
 // the CTA drains instead of hanging.
@@ -163,7 +170,10 @@ __device__ __forceinline__ int fwd_slot_block(const FwdPlan& pl, int s, int e, i
   return (k == heavy) ? -1 : k;
 }
 
-__device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, const FwdPlan& pl, uint32_t mask_flags, int hb, int qt) {
+// bm_t0 / bm_t1: with a host-built block list, the key tiles [t0, t1) that hold every listed block of the rows of
+// Q tile A and B (worked out by a whole warp, see the kernel); unused otherwise.
+__device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, const FwdPlan& pl, uint32_t mask_flags, int hb, int qt,
+                                            const int* bm_t0 = nullptr, const int* bm_t1 = nullptr) {
   FwdItem it;
   const int hpb = p.H / pl.heads;
   it.b = hb / hpb; it.h = (hb % hpb) * pl.heads; it.hk = it.h / p.G; it.q0 = qt * pl.rows;
@@ -182,7 +192,11 @@ __device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, const FwdPlan& 
   for (int X = 0; X < 2; ++X) {
     const int qx = it.q0 + X * pl.q_step;
     t0[X] = 0; t1[X] = 0;
-    if (qx < it.q_lim) {
+    if (qx < it.q_lim && p.bm_count) {
+      // flex.jl:107-182: the list replaces the analytic range (the mask mod still runs per pair, below)
+      t0[X] = bm_t0[X]; t1[X] = min(bm_t1[X], (it.k_len + BN - 1) / BN);
+      if (t1[X] <= t0[X]) { t0[X] = 0; t1[X] = 0; }
+    } else if (qx < it.q_lim) {
       AttnParams pr = p; pr.mask_flags = mask_flags;
       int lo, hi;
       kv_range(pr, qx + p.input_pos, min(qx + BM, p.Sq) - 1 + p.input_pos, it.k_len, &lo, &hi);
@@ -278,6 +292,27 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       const int id0 = __shfl_sync(0xffffffffu, ids[0], 0);
       doc_uniform = __all_sync(0xffffffffu, ids[0] == id0 && ids[1] == id0 && ids[2] == id0 && ids[3] == id0);
     }
+    // Host-built block list (mods.jl:436-476, walk of flex.jl:107-182): state of the (query block, key block) that
+    // each 32-column chunk of this warp's 32 rows lies in, two bits per chunk: 0 not listed (its pairs contribute
+    // nothing), 1 listed (the mask mod decides per pair), 2 listed and marked full (only the key-length bound).
+    // Block edges are multiples of 32, so a warp's rows and a chunk's keys never straddle a block.  32 list
+    // entries per step; the ids of one query block are distinct.
+    const bool listed_walk = MASK == kRuntimeMods && p.bm_count != nullptr;
+    int bst = 0;
+    if (listed_walk) {
+      const int qb = min(wi[WI_Q0] + wq * 32, p.Sq - 1) / p.bm_tm;
+      const int nb = min(p.bm_count[qb], p.bm_stride);
+      for (int base = 0; base < nb; base += 32) {
+        const int t = base + lane;
+        const int j = t < nb ? p.bm_idx[(size_t)qb * p.bm_stride + t] : -1;
+        const bool f = t < nb && p.bm_full[(size_t)qb * p.bm_stride + t] != 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const bool hit = j == (kv0 + q * 32) / p.bm_tn;
+          if (__any_sync(0xffffffffu, hit)) bst |= (__any_sync(0xffffffffu, hit && f) ? 2 : 1) << (2 * q);
+        }
+      }
+    }
     ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::S_FULL + X), (ph0 + i) & 1, abort_flag, &g_attn_fwd_status, 301));
     if (!ok) break;
     tc_fence_after();
@@ -292,8 +327,13 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       tc_fence_before();
       mbar_arrive(bar(SM::P_FULL + X));
     };
-    if ((mask_flags & TYLO_MASK_DOCUMENT) && doc_uniform && __all_sync(0xffffffffu, ids[0] != my_doc)) {
+    if (!listed_walk && (mask_flags & TYLO_MASK_DOCUMENT) && doc_uniform && __all_sync(0xffffffffu, ids[0] != my_doc)) {
       // all 128 keys belong to one document that none of this warp's 32 rows belongs to
+      pass_empty_tile();
+      continue;
+    }
+    if (listed_walk && bst == 0) {
+      // none of the tile's key blocks is listed for this warp's query block
       pass_empty_tile();
       continue;
     }
@@ -303,6 +343,7 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     if (mask_flags & TYLO_MASK_SLIDING) partial = partial || (kv0 < q_hi - p.window);
     if (mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM)) partial = true;
     if (MASK == kRuntimeMods && p.n_or > 0) partial = true;
+    if (listed_walk) partial = true;
     if (mask_flags & TYLO_MASK_DOCUMENT) partial = partial || !doc_uniform || __any_sync(0xffffffffu, ids[0] != my_doc);
     const bool doc_elementwise = (mask_flags & TYLO_MASK_DOCUMENT) && !doc_uniform;
     const bool row_doc_ok = !(mask_flags & TYLO_MASK_DOCUMENT) || doc_elementwise || (__shfl_sync(0xffffffffu, ids[0], 0) == my_doc);
@@ -403,6 +444,16 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
     // element-wise mask (only on tiles that need it: a warp-uniform branch around the whole pass)
     auto apply_mask = [&](uint32_t (&v)[32], const int q) {
       const int sh = q * 32;
+      if (listed_walk) {
+        const int st = (bst >> (2 * q)) & 3;
+        if (st != 1) {
+          // not listed: nothing is kept; marked full: the mask mod is skipped, keys below the length are kept
+          const int lim = st == 2 ? k_len_i - kv0 - sh : 0;
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[t] = (t < lim) ? v[t] : 0xff800000u;
+          return;
+        }
+      }
       if (MASK == kRuntimeMods && p.n_or > 0) {
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
@@ -717,6 +768,29 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     tmem_relinquish();
   }
   if (warp == 2 || warp == 3) {
+    // Block-list launches (one item per CTA): the first spare warp scans the lists of the query blocks under
+    // each Q tile for the smallest and largest key block, 32 entries at a time.
+    int bm_t0[2] = {0, 0}, bm_t1[2] = {0, 0};
+    if (MASK == kRuntimeMods && p.bm_count && warp == 2) {
+      int hb0;
+      const int qt0 = fwd_slot_block(plan, blockIdx.x, 0, hb0);
+#pragma unroll
+      for (int X = 0; X < 2; ++X) {
+        const int qx = qt0 * plan.rows + X * plan.q_step;
+        int lo = 0x7fffffff, hi = -1;
+        if (qx < p.Sq) {
+          for (int qb = qx / p.bm_tm; qb <= (min(qx + BM, p.Sq) - 1) / p.bm_tm; ++qb) {
+            const int nb = min(p.bm_count[qb], p.bm_stride);
+            for (int t = lane; t < nb; t += 32) {
+              const int j = p.bm_idx[(size_t)qb * p.bm_stride + t];
+              lo = min(lo, j); hi = max(hi, j);
+            }
+          }
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo); hi = __reduce_max_sync(0xffffffffu, hi);
+        if (hi >= lo) { bm_t0[X] = lo * p.bm_tn / BN; bm_t1[X] = ((hi + 1) * p.bm_tn + BN - 1) / BN; }
+      }
+    }
     // the item table: thread k of the two spare warps works out item k
     const int k = threadIdx.x - 64;
     if (k < n_local) {
@@ -727,7 +801,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (qt < 0) {
         e[IT_NTOT] = -1;                       // no such entry (middle block of an odd count)
       } else {
-        const FwdItem it = fwd_item(p, plan, mask_flags, hb, qt);
+        const FwdItem it = fwd_item(p, plan, mask_flags, hb, qt, bm_t0, bm_t1);
 #pragma unroll
         for (int X = 0; X < 2; ++X) {
           volatile int* w = e + X * WI_WORDS;
@@ -1001,7 +1075,7 @@ static int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   const long long n_items = nqt * heads * p.B;
   const int sms = sm_count();
   const bool uneven = (p.mask_flags & (TYLO_MASK_SLIDING | TYLO_MASK_DOCUMENT | TYLO_MASK_PREFIX)) != 0 || p.k_lengths ||
-                      p.q_lengths || p.n_or > 0;
+                      p.q_lengths || p.n_or > 0 || p.bm_count;
   int paired = 0;
   long long grid = n_items;
   if (n_items > sms && !uneven) {
@@ -1023,12 +1097,12 @@ static int32_t dispatch_mods(const CUtensorMap& mq, const CUtensorMap& mk, const
   const uint32_t m = p.mask_flags, s = p.score_flags;
   if constexpr (sizeof(T) == 4) {
     // TF32: the plain and the causal forward have their own variants, every mod goes through the run-time one
-    if (p.n_or == 0 && s == 0 && m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, mo, M, L, p, st);
-    if (p.n_or == 0 && s == 0 && m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (p.n_or == 0 && !p.bm_count && s == 0 && m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, mo, M, L, p, st);
+    if (p.n_or == 0 && !p.bm_count && s == 0 && m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, mo, M, L, p, st);
     return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
   } else {
-  // OR-ed clauses and bias tables are handled by the variant that reads its flags at run time
-  if (p.n_or > 0 || (s & TYLO_SCORE_BIAS)) return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
+  // OR-ed clauses, bias tables and block lists are handled by the variant that reads its flags at run time
+  if (p.n_or > 0 || (s & TYLO_SCORE_BIAS) || p.bm_count) return launch_fwd<T, D, kRuntimeMods, kRuntimeMods>(mq, mk, mv, mo, M, L, p, st);
   if (s == 0) {
     if (m == 0) return launch_fwd<T, D, 0, 0>(mq, mk, mv, mo, M, L, p, st);
     if (m == C) return launch_fwd<T, D, C, 0>(mq, mk, mv, mo, M, L, p, st);
