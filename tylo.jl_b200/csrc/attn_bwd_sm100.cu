@@ -121,8 +121,9 @@ __device__ __forceinline__ void tmem_st16x(uint32_t taddr, const uint32_t* r) {
 //   ds_add : gradient at the additive mods' place in the chain (mods.jl:296-303): times (q - kv) it sums
 //            to the ALiBi slope gradient; a soft cap applied after the additive mod is already in it
 template <bool MODDED, bool PARTIAL>
+//   bias : BiasScore's table entry for the pair (mods.jl:219-237), added where ALiBi adds
 __device__ __forceinline__ float element(const AttnParams& p, float c, float slope, float inv_cap, float s, float dp,
-                                         float nlse, float ndelta, int q_minus_kv, bool keep, float& ds0,
+                                         float nlse, float ndelta, int q_minus_kv, bool keep, float bias, float& ds0,
                                          float& ds_add) {
   float pv, f_inner = p.scale, f_outer = 1.f;
   if (MODDED) {
@@ -131,6 +132,7 @@ __device__ __forceinline__ float element(const AttnParams& p, float c, float slo
     const bool cap_first = p.score_flags & TYLO_SCORE_SOFTCAP_FIRST;
     if (cap && cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f_inner *= (1.f - t * t); }
     if (alibi) sm = fmaf(slope, (float)q_minus_kv, sm);
+    if (p.score_flags & TYLO_SCORE_BIAS) sm += bias;
     if (cap && !cap_first) { const float t = tanh_fast(sm * inv_cap); sm = p.cap * t; f_outer = (1.f - t * t); }
     pv = ex2(fmaf(sm, kLog2e, nlse));
   } else {
@@ -148,9 +150,9 @@ __device__ __forceinline__ float element(const AttnParams& p, float c, float slo
 // document comparison: one interval [lo, hi] of row indices of the streamed tensor (queries for a key
 // row in DKDV mode, keys for a query row in DQ mode); mods.jl:101-167 reduced to bounds.
 // k_len: keys of this batch entry that exist; q_lim: query rows below it take part (ragged batches).
-__device__ __forceinline__ bool row_interval(const AttnParams& p, bool keys_own, int own_row, int k_len, int q_lim,
-                                             int* lo_out, int* hi_out) {
-  const uint32_t m = p.mask_flags;
+//   m, window, prefix_len : the conjunction's terms (the mask itself, or one OR-ed clause of it, mods.jl:164-167)
+__device__ __forceinline__ bool row_interval(const AttnParams& p, uint32_t m, int window, int prefix_len, bool keys_own,
+                                             int own_row, int k_len, int q_lim, int* lo_out, int* hi_out) {
   int lo = 0, hi;
   bool any;
   if (keys_own) {                      // own row = key kv, streamed = query rows q (position q + input_pos)
@@ -158,23 +160,25 @@ __device__ __forceinline__ bool row_interval(const AttnParams& p, bool keys_own,
     hi = q_lim - 1;
     any = kv < k_len;
     if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) lo = max(lo, kv - p.input_pos);
-    if (m & TYLO_MASK_SLIDING) hi = min(hi, kv + p.window - p.input_pos);
-    if ((m & TYLO_MASK_PREFIX) && kv >= p.prefix_len) any = false;
-    if ((m & TYLO_MASK_PREFIX_LM) && kv >= p.prefix_len) lo = max(lo, kv - p.input_pos);
+    if (m & TYLO_MASK_SLIDING) hi = min(hi, kv + window - p.input_pos);
+    if ((m & TYLO_MASK_PREFIX) && kv >= prefix_len) any = false;
+    if ((m & TYLO_MASK_PREFIX_LM) && kv >= prefix_len) lo = max(lo, kv - p.input_pos);
   } else {                             // own row = query, streamed = keys
     const int qpos = own_row + p.input_pos;
     hi = k_len - 1;
     any = own_row < q_lim;
     if (m & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) hi = min(hi, qpos);
-    if (m & TYLO_MASK_SLIDING) lo = max(lo, qpos - p.window);
-    if (m & TYLO_MASK_PREFIX) hi = min(hi, p.prefix_len - 1);
-    if (m & TYLO_MASK_PREFIX_LM) hi = min(hi, max(qpos, p.prefix_len - 1));
+    if (m & TYLO_MASK_SLIDING) lo = max(lo, qpos - window);
+    if (m & TYLO_MASK_PREFIX) hi = min(hi, prefix_len - 1);
+    if (m & TYLO_MASK_PREFIX_LM) hi = min(hi, max(qpos, prefix_len - 1));
   }
   *lo_out = lo; *hi_out = hi;
   return any && hi >= lo;
 }
 
-template <typename T, int D, int MODE>
+// ORS: the instantiation that also evaluates OR-ed mask clauses; the common one carries none of that code (with
+// it, the register allocation of the plain element passes changed enough to cost them 3-4 %).
+template <typename T, int D, int MODE, bool ORS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -417,11 +421,24 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     const bool row_ok = (MODE == DKDV) ? (own_row < p.Sk) : (own_row < p.Sq);
     int iv_lo, iv_hi;
-    const bool iv_any = row_interval(p, MODE == DKDV, own_row, k_len, q_lim, &iv_lo, &iv_hi);
+    const bool iv_any = row_interval(p, p.mask_flags, p.window, p.prefix_len, MODE == DKDV, own_row, k_len, q_lim, &iv_lo, &iv_hi);
+    // OR-ed clauses of affine terms (mods.jl:164-167 in disjunctive normal form): one more interval of streamed
+    // rows per clause; a pair is kept if any interval holds it.  (Clauses with a document term run on the
+    // fp32-arithmetic kernels, see the dispatch.)
+    const bool has_or = ORS && p.n_or > 0;
     // ALiBi slope gradient (mods.jl:296-303): the dQ kernel visits every (query, key, head) pair exactly
     // once, so it accumulates sum ds (q - kv) per thread and adds it to d_slopes[h] once per warp.
     const bool want_slope_grad = MODE == DQ && p.d_slopes != nullptr && (p.score_flags & TYLO_SCORE_ALIBI);
     float slope_acc = 0.f;
+    // BiasScore (mods.jl:219-237, gradient :305-313): table (Sk, Sq, heads, batch) indexed by LOCAL rows, heads and
+    // batch broadcast by modulo.  The dQ kernel owns a query row (its keys are contiguous in the table: 16-byte
+    // loads and 16-byte reductions), the dK/dV kernel a key row (one entry per streamed query).  As with the slope
+    // gradient the dQ kernel, which meets every pair once, adds dS at the bias's place in the chain to d_bias.
+    const bool has_bias = (p.score_flags & TYLO_SCORE_BIAS) != 0;
+    const bool want_bias_grad = MODE == DQ && has_bias && p.d_bias != nullptr;
+    const bool bias_vec = (p.Sk & 3) == 0;
+    size_t bias_row = 0;                 // dQ kernel: offset of this query row's entries in the table
+    if (MODE == DQ && has_bias) bias_row = bias_index(p, b, h0, min(own_row, p.Sq - 1), 0);
     const unsigned iv_span = iv_any ? (unsigned)(iv_hi - iv_lo) : 0u;
     // soft cap: tanh(x) ~ x (1 - x^2/3 + 2x^4/15 - 17x^6/315) for |x| < 0.4, written in the raw dot product s (x = s k1)
     const float cap_k1 = p.scale * inv_cap, cap_k2 = p.cap * kLog2e, cap_u = cap_k1 * cap_k1;
@@ -442,6 +459,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool partial = (ka + BT > k_len) || (qa + BT > q_lim) || (p.mask_flags & (TYLO_MASK_PREFIX | TYLO_MASK_PREFIX_LM));
       if (p.mask_flags & (TYLO_MASK_CAUSAL | TYLO_MASK_SLIDING)) partial = partial || (ka + BT - 1 > qa + p.input_pos);
       if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
+      partial = partial || has_or;
 
       ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
       ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T1_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
@@ -484,6 +502,33 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // column j of this warpgroup's half (streamed row tile0 + 64*wg + j) is inside the row's interval
       // iff (unsigned)(j - rel) <= iv_span; a row that pairs with nothing gets an unreachable start
       const int rel = iv_any ? iv_lo - tile0 - 64 * wg : 0x40000000;
+      // (worked out per tile, and only when there are clauses, so that they cost the other paths no registers)
+      int or_rel[kMaxOrClauses]; unsigned or_span[kMaxOrClauses];
+      if (has_or) {
+#pragma unroll
+        for (int ci = 0; ci < kMaxOrClauses; ++ci) {
+          or_rel[ci] = 0x40000000; or_span[ci] = 0u;
+          if (ci < p.n_or) {
+            int lo, hi;
+            const MaskClause& cl = p.or_clause[ci];
+            if (row_interval(p, cl.flags, cl.window, cl.prefix_len, MODE == DKDV, own_row, k_len, q_lim, &lo, &hi)) {
+              or_rel[ci] = lo - tile0 - 64 * wg; or_span[ci] = (unsigned)(hi - lo);
+            }
+          }
+        }
+      }
+      // the element passes exist in three forms: whole tile unmasked (0), one interval per row (1), the interval
+      // plus those of the OR-ed clauses (2)
+      auto keep_at = [&](int j, auto ors_c) -> bool {
+        bool k = (unsigned)(j - rel) <= iv_span;
+        if (decltype(ors_c)::value) {
+#pragma unroll
+          for (int ci = 0; ci < kMaxOrClauses; ++ci) k = k || ((unsigned)(j - or_rel[ci]) <= or_span[ci]);
+        }
+        return k;
+      };
+      using Lvl0 = std::integral_constant<int, 0>; using Lvl1 = std::integral_constant<int, 1>;
+      using Lvl2 = std::integral_constant<int, 2>;
       // position difference q - kv of column j: dpos + j in DKDV mode, dpos - j in DQ mode
       const int dpos = (MODE == DKDV) ? tile0 + 64 * wg + p.input_pos - own_row : own_row + p.input_pos - tile0 - 64 * wg;
 
@@ -493,7 +538,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (!modded) {
         // pass 1 (while the dP MMAs run): p = exp2(c s - lse2), masked; kept in fp32 over sv
         auto pass_p = [&](auto partial_c) {
-          constexpr bool PART = decltype(partial_c)::value;
+          constexpr bool PART = decltype(partial_c)::value != 0;
+          using ORS = std::bool_constant<decltype(partial_c)::value == 2>;
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             uint32_t up[16];
@@ -518,7 +564,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               for (int e = 0; e < 4; ++e) {
                 if (PART) {
                   const int j = q * 32 + t + e;
-                  bool keep = (unsigned)(j - rel) <= iv_span;
+                  bool keep = keep_at(j, ORS{});
                   if (doc_cmp) keep = keep && (doc4[e] == my_doc);
                   if (!keep) pp[e] = 0.f;
                 }
@@ -529,7 +575,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (MODE == DKDV) tmem_st16x(tmem + lane_off + 64 * wg + q * 16, up);
           }
         };
-        if (partial) pass_p(std::true_type{}); else pass_p(std::false_type{});
+        if (!partial) pass_p(Lvl0{}); else if (!has_or) pass_p(Lvl1{}); else pass_p(Lvl2{});
         if (MODE == DKDV) tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(SM::U1_FULL));       // T1 columns released: dV's MMAs / the next S may start
@@ -580,7 +626,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           fastcap = __all_sync(0xffffffffu, fmaxf(am0, am1) * cap_k1 < 0.4f);
         }
         auto run = [&](auto partial_c, auto fast_c) {
-          constexpr bool PART = decltype(partial_c)::value;
+          constexpr bool PART = decltype(partial_c)::value != 0;
+          using ORS = std::bool_constant<decltype(partial_c)::value == 2>;
           constexpr bool FAST = decltype(fast_c)::value;
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
@@ -611,7 +658,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                   float p0 = ex2(x0), p1 = ex2(x1);
                   if (PART) {
                     const int j = q * 32 + t + e;
-                    bool k0 = (unsigned)(j - rel) <= iv_span, k1 = (unsigned)(j + 1 - rel) <= iv_span;
+                    bool k0 = keep_at(j, ORS{}), k1 = keep_at(j + 1, ORS{});
                     if (doc_cmp) { k0 = k0 && (doc4[e] == my_doc); k1 = k1 && (doc4[e + 1] == my_doc); }
                     if (!k0) p0 = 0.f;
                     if (!k1) p1 = 0.f;
@@ -623,16 +670,47 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                   unpack_f32x2(mul_f32x2(mul_f32x2(pack_f32x2(p0, p1), g2), f2), dd[e], dd[e + 1]);
                 }
               } else {
+                float bias4[4] = {0.f, 0.f, 0.f, 0.f}, dsa[4];
+                const int scol = tile0 + col0;        // first of the four streamed rows (keys for dQ, queries for dK/dV)
+                if (has_bias) {
+                  if (MODE == DQ) {
+                    const float* bp = p.bias + bias_row + scol;
+                    if (bias_vec && scol + 3 < p.Sk) {
+                      const float4 f = __ldg(reinterpret_cast<const float4*>(bp));
+                      bias4[0] = f.x; bias4[1] = f.y; bias4[2] = f.z; bias4[3] = f.w;
+                    } else {
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) bias4[e] = (scol + e < p.Sk) ? __ldg(bp + e) : 0.f;
+                    }
+                  } else {
+                    const int kvb = min(own_row, p.Sk - 1);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                      bias4[e] = __ldg(p.bias + bias_index(p, b, h0 + g, min(scol + e, p.Sq - 1), kvb));
+                  }
+                }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const int j = q * 32 + t + e;
-                  bool keep = (unsigned)(j - rel) <= iv_span;
+                  bool keep = keep_at(j, ORS{});
                   if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
                   const int qmk = (MODE == DKDV) ? dpos + j : dpos - j;
-                  float ds_add;
                   pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
-                                              lse4[e], del4[e], qmk, keep, dd[e], ds_add);
-                  if (MODE == DQ && want_slope_grad) slope_acc = fmaf(ds_add, (float)qmk, slope_acc);
+                                              lse4[e], del4[e], qmk, keep, bias4[e], dd[e], dsa[e]);
+                  if (MODE == DQ && want_slope_grad) slope_acc = fmaf(dsa[e], (float)qmk, slope_acc);
+                }
+                if (MODE == DQ && want_bias_grad && own_row < p.Sq) {
+                  // masked pairs and keys beyond the length have p = 0, hence dS = 0: nothing to add there
+                  float* gp = p.d_bias + bias_row + scol;
+                  if (bias_vec && scol + 3 < p.Sk) {
+                    if (dsa[0] != 0.f || dsa[1] != 0.f || dsa[2] != 0.f || dsa[3] != 0.f)
+                      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gp), "f"(dsa[0]), "f"(dsa[1]), "f"(dsa[2]),
+                                   "f"(dsa[3]) : "memory");
+                  } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                      if (scol + e < p.Sk && dsa[e] != 0.f) atomicAdd(gp + e, dsa[e]);
+                  }
                 }
               }
               up[t / 2] = pack16<T>(pp[0], pp[1]); up[t / 2 + 1] = pack16<T>(pp[2], pp[3]);
@@ -643,9 +721,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
         };
         if (fastcap) {
-          if (partial) run(std::true_type{}, std::true_type{}); else run(std::false_type{}, std::true_type{});
+          if (!partial) run(Lvl0{}, std::true_type{}); else if (!has_or) run(Lvl1{}, std::true_type{}); else run(Lvl2{}, std::true_type{});
         } else {
-          if (partial) run(std::true_type{}, std::false_type{}); else run(std::false_type{}, std::false_type{});
+          if (!partial) run(Lvl0{}, std::false_type{}); else if (!has_or) run(Lvl1{}, std::false_type{}); else run(Lvl2{}, std::false_type{});
         }
         tc_wait_st();
         tc_fence_before();
@@ -774,15 +852,16 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
   if (int32_t rc = make_tmap(&mk, K, D, p.Sk, p.Hkv * p.B)) return rc;
   if (int32_t rc = make_tmap(&mv, V, D, p.Sk, p.Hkv * p.B)) return rc;
   if (int32_t rc = make_tmap(&mdo, dO, D, p.Sq, p.H * p.B)) return rc;
+  const bool ors = p.n_or > 0;
   {
-    auto kern = attn_bwd_sm100_kernel<T, D, DKDV>;
+    auto kern = ors ? attn_bwd_sm100_kernel<T, D, DKDV, true> : attn_bwd_sm100_kernel<T, D, DKDV, false>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
     const long long grid = (long long)((p.Sk + BT - 1) / BT) * p.Hkv * p.B;
     kern<<<(unsigned)grid, kThreads, Smem<D>::kDynamic, st>>>(mq, mk, mv, mdo, (T*)dV, (T*)dK, lse2, Delta, p);
     if (int32_t rc = check_launch("attn_bwd_sm100<dkdv>")) return rc;
   }
   {
-    auto kern = attn_bwd_sm100_kernel<T, D, DQ>;
+    auto kern = ors ? attn_bwd_sm100_kernel<T, D, DQ, true> : attn_bwd_sm100_kernel<T, D, DQ, false>;
     TYLO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kDynamic));
     const long long grid = (long long)((p.Sq + BT - 1) / BT) * p.H * p.B;
     // The dQ kernel reads nothing the dK/dV kernel writes (both depend only on the inputs and on the prep

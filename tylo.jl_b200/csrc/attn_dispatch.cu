@@ -15,9 +15,7 @@ static bool or_with_documents(const AttnParams& p) {
   return doc;
 }
 static bool fwd_needs_generic(const AttnParams& p) { return or_with_documents(p); }
-static bool table_mods(const AttnParams& p) {
-  return (p.score_flags & TYLO_SCORE_BIAS) != 0 || p.bm_count != nullptr || p.n_or > 0;
-}
+static bool table_mods(const AttnParams& p) { return p.bm_count != nullptr || or_with_documents(p); }
 
 int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, float* M, float* L,
                           const AttnParams& p, int32_t dtype, cudaStream_t st) {
