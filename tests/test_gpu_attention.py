@@ -55,6 +55,21 @@ def test_shapes(tylo, oracle, shape, causal, dt):
     _run(tylo, oracle, dt, causal=causal, seed=21, **shape)
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [
+    dict(B=2, H=4, Hkv=2, Sq=300, Sk=300, Dk=96, Dv=96),     # padded to the 128-wide tile of the tensor-core kernels
+    dict(B=1, H=3, Hkv=3, Sq=130, Sk=257, Dk=80, Dv=80),
+    dict(B=2, H=2, Hkv=1, Sq=200, Sk=200, Dk=32, Dv=32),     # padded to the 64-wide tile
+    dict(B=1, H=2, Hkv=2, Sq=96, Sk=160, Dk=40, Dv=40),
+    dict(B=1, H=1, Hkv=1, Sq=64, Sk=64, Dk=8, Dv=8),         # one 16-byte packet per row
+])
+@pytest.mark.parametrize("causal", [False, True])
+def test_zero_padded_head_dims(tylo, oracle, shape, causal, dt):
+    """Head dims that are multiples of 8 below 64 / 128 run on the tensor-core kernels with the missing columns
+    read as zeros (the reference pads the same way, attention.jl:241-242); forward, statistics and gradients."""
+    _run(tylo, oracle, dt, causal=causal, seed=33, **shape)
+
+
 def test_config1_fp32(tylo, oracle):
     """Benchmark config 1: fp32, non-causal, D 64, S 512, H 8, B 2, seed 0; <= 1e-5."""
     _run(tylo, oracle, "f32", B=2, H=8, Hkv=8, Sq=512, Sk=512, Dk=64, Dv=64, causal=False, seed=0, bwd=False)

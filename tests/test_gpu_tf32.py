@@ -66,6 +66,8 @@ def test_config1_shape(tylo, oracle, causal):
     dict(B=1, H=6, Hkv=2, Sq=300, Sk=517, D=64),      # odd group size, ragged tile edges, Sq != Sk
     dict(B=2, H=8, Hkv=2, Sq=1024, Sk=1024, D=32),    # head dim 32; more items than one pass of small launches
     dict(B=1, H=2, Hkv=2, Sq=1, Sk=300, D=64),        # single query row
+    dict(B=1, H=4, Hkv=2, Sq=200, Sk=333, D=48),      # zero-padded to the 64-wide tile
+    dict(B=1, H=2, Hkv=2, Sq=96, Sk=96, D=20),        # rows of 80 bytes, padded to the 32-wide tile
 ])
 @pytest.mark.parametrize("causal", [False, True])
 def test_shapes(tylo, oracle, shape, causal):

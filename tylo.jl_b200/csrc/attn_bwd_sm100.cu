@@ -751,7 +751,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                          : ((size_t)(b * p.H + h0) * p.Sq + (row_ok ? own_row : 0));
 #pragma unroll
       for (int a = (MODE == DKDV ? 0 : 1); a < 2; ++a) {
-        T* dst = ((MODE == DKDV) ? (a == 0 ? out1 : out2) : out1) + orow * D + wg * HALF;
+        // (a head dim below the tile's runs zero-padded: rows are p.Dk long, columns beyond are not stored)
+        T* dst = ((MODE == DKDV) ? (a == 0 ? out1 : out2) : out1) + orow * p.Dk + wg * HALF;
 #pragma unroll
         for (int q = 0; q < HALF / 32; ++q) {
           uint32_t acc[32];
@@ -763,7 +764,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ow[t] = (n_iter > 0) ? pack16<T>(__uint_as_float(acc[2 * t]), __uint_as_float(acc[2 * t + 1])) : 0u;
           if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + q * 32 + v * 8) = o4[v];
+            for (int v = 0; v < 4; ++v)
+              if (wg * HALF + q * 32 + v * 8 < p.Dk) *reinterpret_cast<uint4*>(dst + q * 32 + v * 8) = o4[v];
           }
         }
       }
@@ -788,16 +790,17 @@ template <typename T, int LPR>
 __global__ void __launch_bounds__(256)
 bwd_prep_kernel(float* __restrict__ Delta, float* __restrict__ lse2, const T* __restrict__ O,
                 const T* __restrict__ dO, const float* __restrict__ M, const float* __restrict__ L,
-                long long rows, int natural_stats) {
+                long long rows, int natural_stats, int Dr) {
+  // Dr: the rows' real length (a multiple of 8, at most LPR * 8)
   constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31;
   const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
   const int sub = lane % LPR;
   float s = 0.f;
-  if (row < rows) {
+  if (row < rows && sub * 8 < Dr) {
     Pack<T> a, b2;
-    a.raw = ld_stream(O + (size_t)row * (LPR * 8) + sub * 8);
-    b2.raw = ld_stream(dO + (size_t)row * (LPR * 8) + sub * 8);
+    a.raw = ld_stream(O + (size_t)row * Dr + sub * 8);
+    b2.raw = ld_stream(dO + (size_t)row * Dr + sub * 8);
     float fa[8], fb[8];
     a.unpack(fa); b2.unpack(fb);
 #pragma unroll
@@ -845,13 +848,14 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
   const long long rows = (long long)p.Sq * p.H * p.B;
   constexpr int LPR = D / 8, RPB = 8 * (32 / LPR);   // lanes per row, rows per 256-thread block
   bwd_prep_kernel<T, LPR><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(Delta, lse2, (const T*)O, (const T*)dO, M, L,
-                                                                             rows, p.natural_stats);
+                                                                             rows, p.natural_stats, p.Dk);
   if (int32_t rc = check_launch("attn_bwd_prep")) return rc;
   CUtensorMap mq, mk, mv, mdo;
-  if (int32_t rc = make_tmap(&mq, Q, D, p.Sq, p.H * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mk, K, D, p.Sk, p.Hkv * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mv, V, D, p.Sk, p.Hkv * p.B)) return rc;
-  if (int32_t rc = make_tmap(&mdo, dO, D, p.Sq, p.H * p.B)) return rc;
+  // the maps describe the arrays as they are (rows of p.Dk elements); boxes reaching beyond read zeros
+  if (int32_t rc = make_tmap(&mq, Q, p.Dk, p.Sq, p.H * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mk, K, p.Dk, p.Sk, p.Hkv * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mv, V, p.Dk, p.Sk, p.Hkv * p.B)) return rc;
+  if (int32_t rc = make_tmap(&mdo, dO, p.Dk, p.Sq, p.H * p.B)) return rc;
   const bool ors = p.n_or > 0;
   {
     auto kern = ors ? attn_bwd_sm100_kernel<T, D, DKDV, true> : attn_bwd_sm100_kernel<T, D, DKDV, false>;
@@ -885,7 +889,7 @@ static int32_t launch(void* dQ, void* dK, void* dV, const void* Q, const void* K
 
 bool attn_bwd_sm100_supported(const AttnParams& p, int32_t dtype) {
   if (dtype != TYLO_BF16 && dtype != TYLO_F16) return false;
-  if (p.Dk != p.Dv || (p.Dk != 64 && p.Dk != 128)) return false;
+  if (p.Dk != p.Dv || p.Dk < 8 || p.Dk % 8 != 0 || p.Dk > 128) return false;     // below 64 / 128: zero-padded
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2 || (long long)p.Sk * p.Hkv * p.B > 0x7fffffffLL / 2) return false;
   return true;
 }
@@ -900,10 +904,10 @@ int32_t attn_bwd_sm100(void* dQ, void* dK, void* dV, const void* Q, const void* 
                        const AttnParams& p, int32_t dtype, cudaStream_t st) {
   float* lse2 = static_cast<float*>(workspace);
   if (dtype == TYLO_BF16) {
-    if (p.Dk == 128) return bwd::launch<__nv_bfloat16, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+    if (p.Dk > 64) return bwd::launch<__nv_bfloat16, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
     return bwd::launch<__nv_bfloat16, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
   }
-  if (p.Dk == 128) return bwd::launch<__half, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
+  if (p.Dk > 64) return bwd::launch<__half, 128>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
   return bwd::launch<__half, 64>(dQ, dK, dV, Q, K, V, O, dO, M, L, Delta, lse2, p, st);
 }
 

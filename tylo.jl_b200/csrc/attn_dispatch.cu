@@ -28,7 +28,7 @@ int32_t attn_fwd_dispatch(void* O, const void* Q, const void* K, const void* V, 
 // The workspace is sized for the tensor-core path whenever the dtype and head dim could take it
 // (whether a given call does also depends on its optional arguments).
 int64_t attn_bwd_workspace_bytes(int Dk, int Dv, int Sq, int, int H, int, int B, int32_t dtype) {
-  if ((dtype == TYLO_BF16 || dtype == TYLO_F16) && Dk == Dv && (Dk == 64 || Dk == 128))
+  if ((dtype == TYLO_BF16 || dtype == TYLO_F16) && Dk == Dv && Dk >= 8 && Dk % 8 == 0 && Dk <= 128)
     return attn_bwd_sm100_workspace_bytes(Sq, H, B);
   return 0;
 }

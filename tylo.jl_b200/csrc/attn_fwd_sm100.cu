@@ -1052,8 +1052,10 @@ static int32_t make_tmap(CUtensorMap* map, const void* base, int D, int S, int B
 
 bool attn_fwd_sm100_supported(const AttnParams& p, int32_t dtype) {
   if (dtype != TYLO_BF16 && dtype != TYLO_F16 && dtype != TYLO_F32_TF32) return false;
-  if (p.Dk != p.Dv) return false;
-  if (dtype == TYLO_F32_TF32 ? (p.Dk != 32 && p.Dk != 64) : (p.Dk != 64 && p.Dk != 128)) return false;
+  // Head dims below the tile's run zero-padded (attention.jl:241-242): the TMA loads fill the columns beyond the
+  // array with zeros and the stores clip them; a row must be a multiple of 16 bytes for the tensor maps.
+  if (p.Dk != p.Dv || p.Dk < 8) return false;
+  if (dtype == TYLO_F32_TF32 ? (p.Dk % 4 != 0 || p.Dk > 64) : (p.Dk % 8 != 0 || p.Dk > 128)) return false;
   if ((long long)p.Sq * p.H * p.B > 0x7fffffffLL / 2) return false;
   return true;
 }
@@ -1126,14 +1128,14 @@ int32_t attn_fwd_sm100(void* O, const void* Q, const void* K, const void* V, flo
   if (int32_t rc = make_tmap(&mk, K, p.Dk, p.Sk, p.Hkv * p.B, eb)) return rc;
   if (int32_t rc = make_tmap(&mv, V, p.Dv, p.Sk, p.Hkv * p.B, eb, true)) return rc;   // V is the MN-major operand of P V
   if (dtype == TYLO_F32_TF32) {
-    if (p.Dk == 64) return dispatch_mods<float, 64>(mq, mk, mv, mo, M, L, p, st);
+    if (p.Dk > 32) return dispatch_mods<float, 64>(mq, mk, mv, mo, M, L, p, st);
     return dispatch_mods<float, 32>(mq, mk, mv, mo, M, L, p, st);
   }
   if (dtype == TYLO_BF16) {
-    if (p.Dk == 128) return dispatch_mods<__nv_bfloat16, 128>(mq, mk, mv, mo, M, L, p, st);
+    if (p.Dk > 64) return dispatch_mods<__nv_bfloat16, 128>(mq, mk, mv, mo, M, L, p, st);
     return dispatch_mods<__nv_bfloat16, 64>(mq, mk, mv, mo, M, L, p, st);
   }
-  if (p.Dk == 128) return dispatch_mods<__half, 128>(mq, mk, mv, mo, M, L, p, st);
+  if (p.Dk > 64) return dispatch_mods<__half, 128>(mq, mk, mv, mo, M, L, p, st);
   return dispatch_mods<__half, 64>(mq, mk, mv, mo, M, L, p, st);
 }
 
