@@ -47,8 +47,8 @@ typedef enum {
   /* Float32 storage with the matrix products on the tensor cores, operands read as TF32 (sign, exponent,
    * 10 mantissa bits; fp32 accumulation and fp32 softmax) — the reference's default for Float32
    * (`tensorcore = TFloat32`, src/utils.jl:43-44).  Accepted by the attention and flex-attention FORWARD
-   * entry points for head dims 32 and 64; other head dims and OR-ed document terms are computed in true fp32
-   * there.  Every other entry point rejects it: pass TYLO_F32. */
+   * entry points for head dims that are multiples of 4 up to 64; other head dims and OR-ed document terms are
+   * computed in true fp32 there.  Every other entry point rejects it: pass TYLO_F32. */
   TYLO_F32_TF32 = 3
 } tylo_dtype;
 
@@ -175,7 +175,8 @@ int32_t tylo_b200_flex_attention_fwd(void* O, const void* Q, const void* K, cons
  * that are not listed contribute nothing.  bm_count (n_qb), bm_idx and bm_full (n_qb rows of
  * bm_stride entries — the reference's [n_kb, n_qb] column-major arrays) are device int32.
  * tile_m and tile_n must be multiples of 32; n_qb = ceil(Sq / tile_m); the block ids of one query
- * block must be distinct.  16-bit storage with head dim 64 or 128 (and TYLO_F32_TF32 with 32 or 64) walks the
+ * block must be distinct.  16-bit storage with a head dim that is a multiple of 8 up to 128 (and TYLO_F32_TF32
+ * with a multiple of 4 up to 64) walks the
  * list on the tensor-core forward: key tiles from the smallest to the largest listed block, each 32-column chunk
  * of a warp's 32 rows looked up in the list (not listed: nothing kept; full: only the length bound; else the
  * mask mod); everything else runs on the fp32-arithmetic kernel. */

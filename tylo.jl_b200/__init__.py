@@ -717,7 +717,7 @@ def allocate_scratchspace_grad_attention(Q, K, V, O) -> AttnScratch:
 def attention_(O, Q, K, V, *, causal=False, input_pos=0, k_lengths=None, q_lengths=None, checkpoints=None,
                tensorcore=None):
     """attention!(O, Q, K, V; ...) (attention.jl:219-262).  Returns None.  `tensorcore=TFloat32` on Float32
-    arrays: products on the tensor cores with TF32 operands (head dims 32 and 64); default true fp32."""
+    arrays: products on the tensor cores with TF32 operands (head dims up to 64); default true fp32."""
     pO, pQ, pK, pV = primal(O), primal(Q), primal(K), primal(V)
     B, H, Hkv, Sq, Sk, Dk, Dv = _attn_dims(pQ, pK, pV, pO)
     _dense(pO, pQ, pK, pV, k_lengths, q_lengths)

@@ -21,7 +21,7 @@ Fused multi-head attention with GQA.  `Q (Dk,Sq,H,B)`, `K (Dk,Sk,Hkv,B)`, `V (Dv
 `O (Dv,Sq,H,B)`; scale `1/√Dk`.  `checkpoints = allocate_checkpoints(attention!, Q, K, V)` saves the
 softmax statistics for `∇attention!`.  `TILE_M`, `TILE_N` are accepted for source compatibility and ignored
 (tile shapes are fixed per kernel).  `Float32` arrays are computed in true fp32 unless `tensorcore = TFloat32`
-asks for TF32 operands on the tensor cores (head dims 32 and 64).
+asks for TF32 operands on the tensor cores (head dims up to 64).
 Returns `nothing`.
 """
 function attention!(O, Q, K, V; causal = false, input_pos = 0, k_lengths = nothing, q_lengths = nothing,

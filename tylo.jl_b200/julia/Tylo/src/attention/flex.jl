@@ -11,7 +11,7 @@ a fully masked query gives `O = 0`, `M = -Inf`, `L = 0`).  Supported mods: `Caus
 else throws `ArgumentError`.  With `block_mask`
 (a `BlockMask` from `build_block_mask`) the forward walks the host-built block list instead of the
 analytic block range; `TILE_M` / `TILE_N` are the edges the mask was built with (multiples of 32).
-`tensorcore = TFloat32` on `Float32` arrays: TF32 operands on the tensor cores (head dims 32 and 64).
+`tensorcore = TFloat32` on `Float32` arrays: TF32 operands on the tensor cores (head dims up to 64).
 """
 function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMask(), block_mask = nothing,
                          block_sparse = true, input_pos = 0, qk_scale = nothing, tensorcore = nothing,

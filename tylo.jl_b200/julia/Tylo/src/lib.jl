@@ -14,7 +14,7 @@ tylo_dtype(T::Type) = throw(ArgumentError("libtylo_b200 has no kernels for eleme
 
 Value of the `tensorcore` keyword of `attention!` / `flex_attention!` that asks for both matrix products on the
 tensor cores with TF32 operands for `Float32` arrays (the reference's default for `Float32`, utils.jl:43-44).
-The default here, `tensorcore = nothing`, computes `Float32` in true fp32.  Forward only, head dims 32 and 64.
+The default here, `tensorcore = nothing`, computes `Float32` in true fp32.  Forward only, head dims up to 64.
 """
 struct TFloat32 end
 export TFloat32
