@@ -372,6 +372,79 @@ def make_flex(t, torch, seed, bwd=False):
     return w
 
 
+def make_variants(t, torch, seed, which):
+    """Two score / mask variants of the flex path that run on the tensor-core kernels, at sizes of their own
+    (not BASELINE.json configs; recorded so that these paths have a measured number and a parity check):
+      flex_bias_fwd_bwd    BiasScore with a learnable (Sk, Sq, heads) table under a causal mask: forward, backward and
+                           the table's gradient (B 2, H 8, S 2048, D 128; 134 MB table, read by both backward kernels);
+      flex_block_list_fwd  host-built BlockMask (64 x 64 blocks of a causal 512-key window): the forward walks the
+                           list (B 2, H 16, S 4096, D 128)."""
+    import numpy as np
+    sy = synth()
+    BF = torch.bfloat16
+    o = oracle
+    if which == "bias":
+        B, H, S, D = 2, 8, 2048, 128
+        Q, K, V, dO = (sy.normal_cuda(seed, i, (B, H, S, D), BF) for i in range(4))
+        bias = sy.normal_cuda(seed, 4, (1, H, S, S), torch.float32)
+        mod, mask = t.BiasScore(bias), t.CausalMask()
+        O = torch.empty_like(Q)
+        cp = t.allocate_checkpoints_flex_attention(Q, K, V)
+        d_mod = t.grad_shadow(mod)
+        Od, Qd, Kd, Vd = t.Duplicated(O, dO), t.Duplicated(Q), t.Duplicated(K), t.Duplicated(V)
+        sc = t.allocate_scratchspace_grad_flex_attention(Q, K, V, O)
+
+        def step():
+            t.flex_attention_(O, Q, K, V, score_mod=mod, mask_mod=mask, checkpoints=cp)
+            t.grad_flex_attention_(Od, Qd, Kd, Vd, score_mod=mod, mask_mod=mask, d_score_mod=d_mod, checkpoints=cp, scratch=sc)
+
+        def verify():
+            b0, h0 = B - 1, H - 1
+            d_mod.bias.zero_()
+            step()
+            sl = lambda x: f64(x[b0:b0 + 1, h0:h0 + 1])
+            bias64 = f64(bias[:, h0:h0 + 1])
+            kw = dict(score=o().ScoreSpec([("bias", bias64)]), mask=o().MaskSpec(causal=True))
+            ref = o().flex_ref(sl(Q), sl(K), sl(V), **kw)
+            rQ, rK, rV, pg = o().flex_bwd_ref(sl(dO), sl(Q), sl(K), sl(V), **kw)
+            what = f"(batch {b0}, head {h0})"
+            # the table gradient of head h0 sums both batch entries; the oracle slice has one: check dQ, dK, dV and O
+            return worst([parity(O[b0:b0 + 1, h0:h0 + 1], ref, what + " [O]"),
+                          parity(Qd.shadow[b0:b0 + 1, h0:h0 + 1], rQ, what + " [dQ]", grad=True),
+                          parity(Kd.shadow[b0:b0 + 1, h0:h0 + 1], rK, what + " [dK]", grad=True),
+                          parity(Vd.shadow[b0:b0 + 1, h0:h0 + 1], rV, what + " [dV]", grad=True)])
+        pairs = causal_pairs(S) * H * B
+        return dict(name="flex_bias_fwd_bwd", unit="TFLOP/s", bound="tensor", scale=1e-12, launches=4, step=step, verify=verify,
+                    work=14 * D * pairs,
+                    config=dict(workload="flex attention forward + backward with a BiasScore table and its gradient, bf16, causal",
+                                batch=B, seq_len=S, heads=H, head_dim=D, bias_table_bytes=int(bias.numel() * 4)))
+    B, H, S, D, W, T = 2, 16, 4096, 128, 512, 64
+    Q, K, V = (sy.normal_cuda(seed, i, (B, H, S, D), BF) for i in range(3))
+    nqb = S // T
+    cnt = np.zeros(nqb, np.int32); idx = np.zeros((nqb, nqb), np.int32); full = np.zeros((nqb, nqb), np.int32)
+    for i in range(nqb):
+        q_lo, q_hi = i * T, i * T + T - 1
+        js = [j for j in range(nqb) if j * T <= q_hi and j * T + T - 1 >= q_lo - W]
+        cnt[i] = len(js); idx[i, :len(js)] = js
+        full[i, :len(js)] = [int(j * T + T - 1 <= q_lo and j * T >= q_hi - W) for j in js]
+    bm = t.BlockMask(torch.from_numpy(cnt).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(full).cuda(), T, T)
+    mask = t.CausalMask() & t.SlidingWindowMask(W)
+    O = torch.empty_like(Q)
+    q = np.arange(S)
+    pairs = int((q - np.maximum(q - W, 0) + 1).sum()) * H * B
+
+    def verify():
+        b0, h0 = B - 1, H - 1
+        sl = lambda x: f64(x[b0:b0 + 1, h0:h0 + 1])
+        ref = o().flex_block_mask_ref(sl(Q), sl(K), sl(V), cnt, idx, full, TILE_M=T, TILE_N=T,
+                                      mask=o().MaskSpec(causal=True, window=W))
+        return parity(O[b0:b0 + 1, h0:h0 + 1], ref, f"(batch {b0}, head {h0}), every row, against the oracle's block walk")
+    return dict(name="flex_block_list_fwd", unit="TFLOP/s", bound="tensor", scale=1e-12, launches=1, verify=verify,
+                step=lambda: t.flex_attention_(O, Q, K, V, mask_mod=mask, block_mask=bm), work=4 * D * pairs,
+                config=dict(workload="flex attention forward over a host-built block list (64 x 64 blocks, causal 512-key window), bf16",
+                            batch=B, seq_len=S, heads=H, head_dim=D, unmasked_pairs=pairs))
+
+
 def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
     import numpy as np
     sy = synth()
@@ -703,6 +776,8 @@ def main():
         "softmax_bwd": lambda: make_rowwise(t, torch, 1, "softmax_bwd"),
         "mha_fp32": lambda: make_fp32(t, torch, 0),
         "mha_tf32": lambda: make_fp32(t, torch, 0, tf32=True),
+        "flex_bias_fwd_bwd": lambda: make_variants(t, torch, 5, "bias"),
+        "flex_block_list_fwd": lambda: make_variants(t, torch, 6, "block_list"),
     }
 
     def roofline(w, ms):
