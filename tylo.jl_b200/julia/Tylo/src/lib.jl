@@ -20,9 +20,10 @@ struct TFloat32 end
 export TFloat32
 
 "Element-type code of a forward attention call: `Float32` arrays with `tensorcore = TFloat32` run as TF32."
-fwd_dtype(T::Type, tensorcore) =
-    (T === Float32 && tensorcore !== nothing && nameof(tensorcore) === :TFloat32) ? Int32(3) : tylo_dtype(T)
-fwd_dtype(T::Type, ::Nothing) = tylo_dtype(T)
+fwd_dtype(T::Type, tensorcore) = (T === Float32 && is_tf32(tensorcore)) ? Int32(3) : tylo_dtype(T)
+is_tf32(x::Type) = nameof(x) === :TFloat32        # this package's marker or another package's type of that name
+is_tf32(x::Symbol) = x === :TFloat32 || x === :tf32
+is_tf32(x) = false
 
 # ---- the three version-dependent spellings -------------------------------------------------
 """
