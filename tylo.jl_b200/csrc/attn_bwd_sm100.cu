@@ -461,6 +461,27 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (p.mask_flags & TYLO_MASK_SLIDING) partial = partial || (ka < qa + BT - 1 + p.input_pos - p.window);
       partial = partial || has_or;
 
+      if (has_bias && n + 1 < n_iter) {
+        // The next tile's block of the bias table, asked for a tile ahead so that it waits in L2: the element pass
+        // reads it four entries at a time and would otherwise sit out a DRAM round trip for each.  dQ: this query
+        // row's 128 entries (four lines); dK/dV: the line of this warp's 32 keys for each of the 128 queries,
+        // four per lane.
+        const int n1 = n + 1;
+        const int t1 = (it_lo + ((MODE == DKDV) ? n1 % it_n : n1)) * BT;
+        if (MODE == DQ) {
+          const float* bn = p.bias + bias_row + min(t1, p.Sk - 1);
+#pragma unroll
+          for (int cl = 0; cl < 4; ++cl)
+            if (t1 + cl * 32 < p.Sk) asm volatile("prefetch.global.L2 [%0];" ::"l"(bn + cl * 32));
+        } else {
+          const int g1 = n1 / it_n, kvb = min(own_row, p.Sk - 1);
+#pragma unroll
+          for (int cl = 0; cl < 4; ++cl) {
+            const int qn = t1 + cl * 32 + lane;
+            if (qn < p.Sq) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.bias + bias_index(p, b, h0 + g1, qn, kvb)));
+          }
+        }
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(SM::STAT_FULL + s), (n / kStages) & 1, abort_flag, &g_attn_bwd_status, 301));
       ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(SM::T1_FULL), n & 1, abort_flag, &g_attn_bwd_status, 302));
       if (!ok) break;
@@ -531,6 +552,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       using Lvl2 = std::integral_constant<int, 2>;
       // position difference q - kv of column j: dpos + j in DKDV mode, dpos - j in DQ mode
       const int dpos = (MODE == DKDV) ? tile0 + 64 * wg + p.input_pos - own_row : own_row + p.input_pos - tile0 - 64 * wg;
+      const float fdpos = (float)dpos;
 
       // Each warpgroup writes its packed 16-bit columns over the first half of ITS OWN 64 T columns
       // (the MMA addresses the two 32-column pieces separately), so no thread overwrites T values
@@ -628,7 +650,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         auto run = [&](auto partial_c, auto fast_c) {
           constexpr bool PART = decltype(partial_c)::value != 0;
           using ORS = std::bool_constant<decltype(partial_c)::value == 2>;
-          constexpr bool FAST = decltype(fast_c)::value;
+          // kind of score-mod evaluation: 0 the general chain, 1 soft cap alone with small scores (polynomial), 2 additive
+          // mods only (ALiBi, bias table): one exponent per element, no run-time flag tests, no conversions
+          constexpr int KIND = decltype(fast_c)::value;
+          constexpr bool FAST = KIND == 1;
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             uint32_t up[16], ud[16];
@@ -694,10 +719,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                   const int j = q * 32 + t + e;
                   bool keep = keep_at(j, ORS{});
                   if (PART && doc_cmp) keep = keep && (doc4[e] == my_doc);
-                  const int qmk = (MODE == DKDV) ? dpos + j : dpos - j;
-                  pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
-                                              lse4[e], del4[e], qmk, keep, bias4[e], dd[e], dsa[e]);
-                  if (MODE == DQ && want_slope_grad) slope_acc = fmaf(dsa[e], (float)qmk, slope_acc);
+                  if (KIND == 2) {
+                    // exponent = s c + (slope (q - kv) + bias) log2e - lse2;  dS at the mods' place = p (dP - Delta)
+                    const float pos = (MODE == DKDV) ? fdpos + (float)j : fdpos - (float)j;
+                    float pv = ex2(fmaf(__uint_as_float(sv[q][t + e]), c, fmaf(fmaf(slope, pos, bias4[e]), kLog2e, lse4[e])));
+                    if (PART && !keep) pv = 0.f;
+                    dsa[e] = pv * (__uint_as_float(dv[q][t + e]) + del4[e]);
+                    dd[e] = dsa[e] * p.scale;
+                    pp[e] = pv;
+                    if (MODE == DQ && want_slope_grad) slope_acc = fmaf(dsa[e], pos, slope_acc);
+                  } else {
+                    const int qmk = (MODE == DKDV) ? dpos + j : dpos - j;
+                    pp[e] = element<true, PART>(p, c, slope, inv_cap, __uint_as_float(sv[q][t + e]), __uint_as_float(dv[q][t + e]),
+                                                lse4[e], del4[e], qmk, keep, bias4[e], dd[e], dsa[e]);
+                    if (MODE == DQ && want_slope_grad) slope_acc = fmaf(dsa[e], (float)qmk, slope_acc);
+                  }
                 }
                 if (MODE == DQ && want_bias_grad && own_row < p.Sq) {
                   // masked pairs and keys beyond the length have p = 0, hence dS = 0: nothing to add there
@@ -721,9 +757,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
         };
         if (fastcap) {
-          if (!partial) run(Lvl0{}, std::true_type{}); else if (!has_or) run(Lvl1{}, std::true_type{}); else run(Lvl2{}, std::true_type{});
+          if (!partial) run(Lvl0{}, Lvl1{}); else if (!has_or) run(Lvl1{}, Lvl1{}); else run(Lvl2{}, Lvl1{});
+        } else if (!(p.score_flags & (TYLO_SCORE_SOFTCAP | TYLO_SCORE_SOFTCAP_FIRST))) {
+          if (!partial) run(Lvl0{}, Lvl2{}); else if (!has_or) run(Lvl1{}, Lvl2{}); else run(Lvl2{}, Lvl2{});
         } else {
-          if (!partial) run(Lvl0{}, std::false_type{}); else if (!has_or) run(Lvl1{}, std::false_type{}); else run(Lvl2{}, std::false_type{});
+          if (!partial) run(Lvl0{}, Lvl0{}); else if (!has_or) run(Lvl1{}, Lvl0{}); else run(Lvl2{}, Lvl0{});
         }
         tc_wait_st();
         tc_fence_before();

@@ -292,6 +292,28 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       const int id0 = __shfl_sync(0xffffffffu, ids[0], 0);
       doc_uniform = __all_sync(0xffffffffu, ids[0] == id0 && ids[1] == id0 && ids[2] == id0 && ids[3] == id0);
     }
+    // BiasScore (mods.jl:219-237): this row's 32 table entries for chunk q, local row index, heads and batch
+    // broadcast by modulo; 16-byte loads when the row start is aligned, guarded scalars otherwise.  Asked for a
+    // chunk ahead of their use (the first chunk before the scores are even there), so that the latency of the
+    // table is not in the tile's chain.
+    const bool has_bias = MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS);
+    auto load_bias = [&](float (&bias_row)[32], const int q) {
+      if (!has_bias) return;
+      const int kvq = kv0 + q * 32;
+      const float* bp = p.bias + bias_index(p, wi[WI_B], wi[WI_H], min(wi[WI_Q0] + r, p.Sq - 1), 0);
+      if ((p.Sk & 3) == 0 && kvq + 32 <= p.Sk) {
+#pragma unroll
+        for (int t = 0; t < 32; t += 4) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(bp + kvq + t));
+          bias_row[t] = f.x; bias_row[t + 1] = f.y; bias_row[t + 2] = f.z; bias_row[t + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
+      }
+    };
+    float bias_a[32], bias_b[32];      // two chunks of table entries in flight (bias tables only)
+    load_bias(bias_a, 0);
     // Host-built block list (mods.jl:436-476, walk of flex.jl:107-182): state of the (query block, key block) that
     // each 32-column chunk of this warp's 32 rows lies in, two bits per chunk: 0 not listed (its pairs contribute
     // nothing), 1 listed (the mask mod decides per pair), 2 listed and marked full (only the key-length bound).
@@ -386,7 +408,7 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
 
     // ---- the steps of one chunk: 32 key columns (chunk q of the tile) of this thread's row ----
     // score mods (compile-time selected)
-    auto apply_mods = [&](uint32_t (&v)[32], const int q) {
+    auto apply_mods = [&](uint32_t (&v)[32], const int q, const float (&bias_row)[32]) {
       if (score_flags == TYLO_SCORE_SOFTCAP) {
         // Soft cap alone: if every score of the warp's rows is small against the cap (the usual case),
         // tanh is a branch-free odd polynomial on the FMA pipe for the whole chunk.
@@ -411,25 +433,27 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
           return;
         }
       }
-      // BiasScore (mods.jl:219-237): this row's 32 table entries for the chunk, local row index, heads and
-      // batch broadcast by modulo; 16-byte loads when the row start is aligned, guarded scalars otherwise.
-      float bias_row[32];
       const int kvq = kv0 + q * 32;
-      if (MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS)) {
-        const int row_b = min(wi[WI_Q0] + r, p.Sq - 1);
-        const float* bp = p.bias + bias_index(p, wi[WI_B], wi[WI_H], row_b, 0);
-        if ((p.Sk & 3) == 0 && kvq + 32 <= p.Sk) {
+      const int qpos = wi[WI_Q0] + r + p.input_pos;
+      if (!(score_flags & TYLO_SCORE_SOFTCAP)) {
+        // Additive mods only (ALiBi, bias tables): one fused multiply-add per element and mod, in log2 units, no
+        // per-element tests of flags that are only known at run time, no integer-to-float conversion (the
+        // position difference of column t is that of column 0 minus t).
+        const float k2 = p.scale * kLog2e;
+        if (score_flags & TYLO_SCORE_ALIBI) {
+          const float sl2 = slope * kLog2e, d0 = (float)(qpos - kvq);
+          const bool bias_too = MASK == kRuntimeMods && (score_flags & TYLO_SCORE_BIAS);
 #pragma unroll
-          for (int t = 0; t < 32; t += 4) {
-            const float4 f = __ldg(reinterpret_cast<const float4*>(bp + kvq + t));
-            bias_row[t] = f.x; bias_row[t + 1] = f.y; bias_row[t + 2] = f.z; bias_row[t + 3] = f.w;
+          for (int t = 0; t < 32; ++t) {
+            const float add = fmaf(sl2, d0 - (float)t, bias_too ? bias_row[t] * kLog2e : 0.f);
+            v[t] = __float_as_uint(fmaf(__uint_as_float(v[t]), k2, add));
           }
         } else {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) bias_row[t] = (kvq + t < p.Sk) ? __ldg(bp + kvq + t) : 0.f;
+          for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(fmaf(__uint_as_float(v[t]), k2, bias_row[t] * kLog2e));
         }
+        return;
       }
-      const int qpos = wi[WI_Q0] + r + p.input_pos;
       const bool cap_first = score_flags & TYLO_SCORE_SOFTCAP_FIRST;
 #pragma unroll
       for (int t = 0; t < 32; ++t) {
@@ -497,7 +521,7 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       tc_wait_ld();
       if (modded) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) apply_mods(sr[q], q);
+        for (int q = 0; q < 4; ++q) apply_mods(sr[q], q, bias_a);      // (never a bias table in this form)
       }
       if (partial) {
 #pragma unroll
@@ -516,13 +540,14 @@ __device__ __forceinline__ bool softmax_tile(const AttnParams& p, const uint32_t
       for (int h = 0; h < 2; ++h) {
         const int qa = 2 * h, qb = 2 * h + 1;
         tmem_ld32(ts + qb * 32, b);
-        if (modded) apply_mods(a, qa);
+        load_bias(bias_b, qb);
+        if (modded) apply_mods(a, qa, bias_a);
         if (partial) apply_mask(a, qa);
         mxa = fmaxf(mxa, chunk_max(a));
         if (changed) tmem_st32(ts + qa * 32, a);
         tc_wait_ld_for(b);
-        if (h == 0) tmem_ld32(ts + 64, a);
-        if (modded) apply_mods(b, qb);
+        if (h == 0) { tmem_ld32(ts + 64, a); load_bias(bias_a, 2); }
+        if (modded) apply_mods(b, qb, bias_b);
         if (partial) apply_mask(b, qb);
         mxb = fmaxf(mxb, chunk_max(b));
         if (changed) tmem_st32(ts + qb * 32, b);
