@@ -803,7 +803,7 @@ def flex_attention_(O, Q, K, V, *, score_mod=None, mask_mod=None, block_mask=Non
         _check(_lib.tylo_b200_flex_attention_fwd_block_mask(
             _p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md), ctypes.byref(sd), _p(bm.count), _p(bm.idx),
             _p(bm.full), int(bm.idx.shape[1]), int(bm.TILE_M), int(bm.TILE_N), Dk, Dv, Sq, Sk, H, Hkv, B,
-            int(input_pos), 0.0 if qk_scale is None else float(qk_scale), _dtype(pQ), _stream()))
+            int(input_pos), 0.0 if qk_scale is None else float(qk_scale), _fwd_dtype(pQ, tensorcore), _stream()))
         return
     _check(_lib.tylo_b200_flex_attention_fwd(_p(pO), _p(pQ), _p(pK), _p(pV), _p(M), _p(L), ctypes.byref(md),
                                              ctypes.byref(sd), Dk, Dv, Sq, Sk, H, Hkv, B, int(input_pos),

@@ -36,7 +36,7 @@ function flex_attention!(O, Q, K, V; score_mod = NoOpScore(), mask_mod = FullMas
                 devptr(pO), devptr(pQ), devptr(pK), devptr(pV), devptr(M), devptr(L), md, sd,
                 devptr(bm.count), devptr(bm.idx), devptr(bm.full), Int32(size(bm.idx, 1)), Int32(TILE_M), Int32(TILE_N),
                 Dk, Dv, Sq, Sk, H, Hkv, B, Int32(input_pos), qk_scale === nothing ? 0.0f0 : Float32(qk_scale),
-                tylo_dtype(eltype(pQ)), current_stream()))
+                fwd_dtype(eltype(pQ), tensorcore), current_stream()))
         end
         return
     end
