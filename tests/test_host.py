@@ -158,3 +158,21 @@ def test_adapt_rebuilds_mods(tylo):
     assert isinstance(m, t.AndMask) and m.b.doc_q.dtype == torch.int64 and t.hmask(m, 3, 3) and not t.hmask(m, 3, 2)
     s = t.adapt(lambda x: x * 2, t.SoftCapScore(5.0) @ t.AliBiScore(torch.ones(2)))
     assert s.b.cap == 5.0 and float(s.a.slopes[0]) == 2.0
+
+
+def test_tensorcore_keyword_maps_to_the_dtype_code(tylo):
+    """`tensorcore = TFloat32` asks for TF32 operands on Float32 storage only (utils.jl:43-44: the reference's default);
+    16-bit storage keeps its own code, None keeps true fp32, anything else is refused."""
+    t = tylo
+    f32, bf = torch.empty(1, dtype=torch.float32), torch.empty(1, dtype=torch.bfloat16)
+    assert t._fwd_dtype(f32, None) == t.F32
+    assert t._fwd_dtype(f32, t.TFloat32) == t.F32_TF32 == 3
+    assert t._fwd_dtype(f32, "tf32") == t.F32_TF32
+    assert t._fwd_dtype(bf, t.TFloat32) == t.BF16
+    assert t._fwd_dtype(f32, "Float32") == t.F32
+
+    class TFloat32:          # a type of that name from another package
+        pass
+    assert t._fwd_dtype(f32, TFloat32) == t.F32_TF32
+    with pytest.raises(ValueError):
+        t._fwd_dtype(f32, "fp8")
