@@ -556,6 +556,59 @@ def make_decode(t, torch, seed, long_ctx, rank=0, world=1, dist=None):
     return w
 
 
+def make_decode_heads(t, torch, seed, rank, world):
+    """Config 5b cut the other way: the 8 KV heads (with their query heads) are divided over the GPUs, every GPU
+    keeps ALL 1,048,576 keys of its heads.  The same bytes per GPU as the key-range sharding of `decode_1m`, but
+    the GPUs' outputs are disjoint (query heads), so there is nothing to exchange — the layout a tensor-parallel
+    decoder has anyway (heads sharded, the output projection row-parallel).  Only divides as far as the KV heads
+    go (8).  Strong scaling: value = the whole cache's bytes / the slowest rank's step."""
+    import numpy as np
+    sy = synth()
+    c = C5B
+    BF = torch.bfloat16
+    B, H, Hkv, D, S = c["B"], c["H"], c["Hkv"], c["D"], c["S"]
+    G = H // Hkv
+    if Hkv % world != 0:
+        raise ValueError(f"{Hkv} KV heads do not divide over {world} GPUs")
+    hk_n = Hkv // world
+    hk0 = rank * hk_n
+    Qall = sy.normal_cuda(seed, 10, (B, H, D), BF)
+    Q = Qall[:, hk0 * G:(hk0 + hk_n) * G].contiguous()
+    K = torch.empty(B, hk_n, S, D, device="cuda", dtype=BF); V = torch.empty_like(K)
+    for i in range(hk_n):
+        a = ((hk0 + i) * S) * D
+        K[0, i] = sy.normal_cuda(seed, 11, (S, D), BF, start=a)
+        V[0, i] = sy.normal_cuda(seed, 12, (S, D), BF, start=a)
+    lengths = torch.full((B,), S, dtype=torch.int32, device="cuda")
+    O = torch.empty_like(Q)
+    n_splits = t.decode_suggest_splits(S, hk_n, B)
+    sc = t.allocate_scratchspace_decode_attention(O, Q, n_splits=n_splits)
+    kv_bytes = S * B * Hkv * 2 * D * 2
+    eager = lambda: t.decode_attention_(O, Q, K, V, lengths=lengths, scratch=sc)
+    step, graphed = eager, False
+    if world > 1:
+        eager(); torch.cuda.synchronize()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                eager()
+            step, graphed = graph.replay, True
+        except Exception:
+            step = eager
+
+    def verify():
+        i = hk_n - 1
+        hs = slice(i * G, (i + 1) * G)
+        ref = oracle().decode_reference(f64(Q[:, hs]), f64(K[:, i:i + 1]), f64(V[:, i:i + 1]), [S])
+        return parity(O[:, hs], ref, f"rank {rank}: the {G} query heads of kv head {hk0 + i}, all {S} keys")
+    w = dict(name="decode_1m_heads", unit="GB/s", bound="hbm", scale=1e-9, launches=1, step=step, verify=verify,
+             work=kv_bytes // world, global_work=kv_bytes, verify_all_ranks=True,
+             config=dict(workload="split-KV decode, bf16, 1 sequence x 1,048,576 keys, KV heads divided over the GPUs (no exchange)",
+                         heads_q=H, heads_kv=Hkv, head_dim=D, kv_heads_per_gpu=hk_n, n_splits=n_splits, live_kv_bytes=kv_bytes,
+                         cuda_graph=graphed))
+    return w
+
+
 def make_rowwise(t, torch, seed, kind):
     """Row kernels, forward (`softmax`, `rms_norm`, `layer_norm`) and backward (`*_bwd`).  Algorithmic bytes:
     forward one read + one write of the matrix; backward two reads (the saved tensor and the incoming
@@ -768,6 +821,7 @@ def main():
         "flex_bwd": lambda: make_flex(t, torch, 3, bwd=True),
         "decode_ragged": lambda: make_decode(t, torch, 4, False),
         "decode_1m": lambda: make_decode(t, torch, 4, True, rank, world, dist),
+        "decode_1m_heads": lambda: make_decode_heads(t, torch, 4, rank, world),
         "rms_norm": lambda: make_rowwise(t, torch, 1, "rms_norm"),
         "layer_norm": lambda: make_rowwise(t, torch, 1, "layer_norm"),
         "softmax": lambda: make_rowwise(t, torch, 1, "softmax"),

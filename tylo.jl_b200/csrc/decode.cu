@@ -760,12 +760,16 @@ using namespace tylo;
 extern "C" int32_t tylo_b200_decode_suggest_splits(int32_t Sk, int32_t Hkv, int32_t B) {
   if (Sk <= 0 || Hkv <= 0 || B <= 0) return 1;
   const int64_t groups = (int64_t)Hkv * B;
-  // Eight CTAs' worth of work per SM when that still leaves a split a couple of thousand keys (measured best
-  // from 512 Ki keys per GPU upwards: CTAs that finish early make room for the rest); for shorter caches one
-  // resident wave of two CTAs per SM, whose fixed cost per CTA (start-up, the closing merge) is paid once
-  // (measured on a 131,072-key shard: 83 us against 95 us with eight per SM in the one-launch form).
-  int64_t target = (int64_t)sm_count() * 8;
-  if ((int64_t)Sk * groups < target * 2048) target = (int64_t)sm_count() * 2;
+  // CTAs per SM by the size of the cache (keys x KV heads x batch; 512 bytes each at head dim 128), measured with
+  // the one-launch form, back-to-back launches on rotating buffers:
+  //   up to ~0.8 GB   one CTA per SM: start-up and the closing merge are paid once per SM and the merge stays narrow
+  //                   (537 MB as 8 heads x 131,072 keys: 77-84 us against 83-85 with two per SM and 98 with eight;
+  //                   as ONE head x 1,048,576 keys: 75-80 us with 148 splits against 94 with 296 and 183 with 1,184);
+  //   up to ~3 GB     four per SM (1.07 GB: 162 us against 173 with one; 2.1 GB: 311 against 329);
+  //   above           eight per SM: CTAs that finish early make room for the rest (4.3 GB: 602 us against 657).
+  const int64_t key_heads = (int64_t)Sk * groups;
+  const int per_sm = key_heads < 1536 * 1024 ? 1 : (key_heads < 6 * 1024 * 1024 ? 4 : 8);
+  const int64_t target = (int64_t)sm_count() * per_sm;
   int64_t n = (target + groups - 1) / groups;
   const int64_t max_by_len = (Sk + 255) / 256;          // keep at least 256 keys per split
   if (n > max_by_len) n = max_by_len;
