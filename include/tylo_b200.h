@@ -88,8 +88,11 @@ typedef struct tylo_mask_desc {
   int64_t doc_kv_len;
   const struct tylo_mask_desc* or_next; /* OrMask (mods.jl:164-167): NULL, or another conjunction OR-ed with this
                                            one — a mask tree is passed in disjunctive normal form, at most 4
-                                           clauses.  Masks with more than one clause run on the fp32-arithmetic
-                                           kernels without block skipping.  prefix_lm keeps its own flag. */
+                                           clauses.  Clauses of affine terms (causal, window, prefix) run on the
+                                           tensor-core kernels as one key interval per clause and row; a clause
+                                           with a DOCUMENT term sends the call to the fp32-arithmetic kernels.
+                                           No block skipping with more than one clause.  prefix_lm keeps its own
+                                           flag. */
 } tylo_mask_desc;
 
 #define TYLO_SCORE_ALIBI 1u         /* AliBiScore: s + slopes[h] * (q - kv), one slope per query head (mods.jl:205-209) */
