@@ -233,6 +233,58 @@ softmax_bwd_kernel(T* __restrict__ dX, const T* __restrict__ dY, const T* __rest
   y.store(dX + row * M + begin, nvec);
 }
 
+// Long rows, backward: two passes over Y and dY instead of a register-resident row.  Pass 1 sums y * dy, pass 2
+// reads both again — a row pair is 128 KB at 32,768 16-bit elements, a few hundred of them in flight fit L2 many
+// times over, so the second read never reaches HBM — and writes dX.  No cluster, no row held in registers: a thread
+// keeps eight 16-byte loads in flight and the CTA is free of the all-or-nothing scheduling of a cluster.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+softmax_bwd_twopass_kernel(T* __restrict__ dX, const T* __restrict__ dY, const T* __restrict__ Y, int64_t M) {
+  constexpr int VEC = Elem<T>::kVec;
+  __shared__ float smem[32];
+  const size_t base = (size_t)blockIdx.x * M;
+  const int nvec = (int)(M / VEC);
+  const uint4* y4 = reinterpret_cast<const uint4*>(Y + base);
+  const uint4* d4 = reinterpret_cast<const uint4*>(dY + base);
+  float dot = 0.f;
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * THREADS) {
+    Pack<T> y[4], d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * THREADS;
+      y[u].raw = v < nvec ? __ldg(y4 + v) : make_uint4(0, 0, 0, 0);
+      d[u].raw = v < nvec ? __ldg(d4 + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float a[VEC], b[VEC];
+      y[u].unpack(a); d[u].unpack(b);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) dot = fmaf(a[j], b[j], dot);
+    }
+  }
+  dot = block_reduce<THREADS>(dot, SumOp(), 0.f, smem);
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * THREADS) {
+    Pack<T> y[4], d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * THREADS;
+      y[u].raw = v < nvec ? __ldg(y4 + v) : make_uint4(0, 0, 0, 0);
+      d[u].raw = v < nvec ? __ldg(d4 + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * THREADS;
+      float a[VEC], b[VEC];
+      y[u].unpack(a); d[u].unpack(b);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) a[j] = a[j] * (b[j] - dot);
+      y[u].pack(a);
+      if (v < nvec) st_stream(dX + base + (size_t)v * VEC, y[u].raw);
+    }
+  }
+}
+
 // Any M, any alignment: online max/sum pass, then a second pass that re-reads X (mostly from L2).
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -317,6 +369,14 @@ static int32_t softmax_launch(void* out, const void* a, const void* b, int64_t M
     if (nvec <= 256) TYLO_SM_LAUNCH(128, 2);
     if (nvec <= kPartVec) TYLO_SM_LAUNCH(256, 4);
 #undef TYLO_SM_LAUNCH
+    if constexpr (!FWD) {
+      // rows too long for one CTA's registers: the two-pass form (4,952 GB/s with the clustered register-resident
+      // form on 4096 x 32768 bf16, 6,225 with this one at 1,024 threads; 5,317 at 512 and 4,042 at 256 threads)
+      if (nvec > kPartVec) {
+        softmax_bwd_twopass_kernel<T, 1024><<<(unsigned)N, 1024, 0, st>>>((T*)out, (const T*)a, (const T*)b, M);
+        return check_launch(what);
+      }
+    }
     if (nvec <= 8 * kPartVec && N * 8 <= 0x7fffffffLL) {
       unsigned c = 2;
       while ((int64_t)c * kPartVec < nvec) c *= 2;
