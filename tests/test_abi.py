@@ -124,3 +124,19 @@ def test_block_mask_and_or_chain_validation(tylo):
     rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(chain[0]), ctypes.byref(sd),
                                           64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
     assert rc == 1 and b"DocumentMask" in lib.tylo_b200_last_error()
+
+
+def test_decode_split_suggestion_follows_the_cache_size():
+    """`tylo_b200_decode_suggest_splits` needs no GPU: without one it assumes 148 SMs.  One CTA per SM below ~0.8 GB
+    of cache (keys x KV heads x batch < 1.5 Mi), four up to ~3 GB, eight above; never fewer than 256 keys per split."""
+    import ctypes
+    from pathlib import Path
+    lib = ctypes.CDLL(str(Path(__file__).resolve().parent.parent / "tylo.jl_b200" / "libtylo_b200.so"))
+    f = lib.tylo_b200_decode_suggest_splits
+    assert f(131072, 8, 1) == 19          # 537 MB as 8 heads x 131,072 keys: 148 CTAs
+    assert f(1 << 20, 1, 1) == 148        # 537 MB as one head x 1,048,576 keys
+    assert f(262144, 8, 1) == 74          # 1.07 GB: four per SM
+    assert f(1 << 20, 8, 1) == 148        # 4.3 GB: eight per SM
+    assert f(32768, 8, 64) == 3           # the ragged batch: eight per SM over 512 groups
+    assert f(100, 1, 1) == 1 and f(0, 1, 1) == 1
+    assert f(300, 1, 1) == 2              # at least 256 keys per split
