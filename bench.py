@@ -580,10 +580,9 @@ def make_decode_heads(t, torch, seed, rank, world):
     BF = torch.bfloat16
     B, H, Hkv, D, S = c["B"], c["H"], c["Hkv"], c["D"], c["S"]
     G = H // Hkv
-    if Hkv % world != 0:
-        raise ValueError(f"{Hkv} KV heads do not divide over {world} GPUs")
-    hk_n = Hkv // world
-    hk0 = rank * hk_n
+    sharding = load_by_path("tylo_b200_sharding", ROOT / "tylo.jl_b200" / "sharding.py")
+    hk0, hk1, _, _ = sharding.head_shard(Hkv, G, rank, world)
+    hk_n = hk1 - hk0
     Qall = sy.normal_cuda(seed, 10, (B, H, D), BF)
     Q = Qall[:, hk0 * G:(hk0 + hk_n) * G].contiguous()
     K = torch.empty(B, hk_n, S, D, device="cuda", dtype=BF); V = torch.empty_like(K)

@@ -37,6 +37,9 @@ def test_partitions_tile_the_work():
     assert sharding.prefill_shard(8, 4, 0, 1) == [(0, 0, 8), (1, 0, 8), (2, 0, 8), (3, 0, 8)]
     # config 5b: 1,048,576 keys over 8 GPUs
     assert [sharding.kv_shard(1 << 20, r, 8) for r in (0, 7)] == [(0, 131072), (917504, 1048576)]
+    assert [sharding.head_shard(8, 8, r, 4) for r in (0, 3)] == [(0, 2, 0, 16), (6, 8, 48, 64)]
+    with pytest.raises(ValueError):
+        sharding.head_shard(8, 8, 0, 3)
     spans = [sharding.kv_shard(1000, r, 3) for r in range(3)]
     assert spans[0][0] == 0 and spans[-1][1] == 1000 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
     with pytest.raises(ValueError):

@@ -2,10 +2,12 @@
 crosses NVLink in the sharded decode.  Pure Python/torch: no device work happens here, so the same
 code runs under gloo on CPU ranks in the tests and under NCCL on GPUs in the benchmark.
 
-Only two shardings exist (the reference itself is single-GPU):
+The shardings (the reference itself is single-GPU):
   * prefill forward/backward: (kv-head, batch) units are independent -> contiguous ranges, no exchange;
   * long-context decode: contiguous key ranges -> one all-gather of (O, max, sum) partials, then the
-    same log-sum-exp merge the split kernel's combine uses (src/attention/decode.jl:119-140)."""
+    same log-sum-exp merge the split kernel's combine uses (src/attention/decode.jl:119-140);
+  * long-context decode the other way: KV heads divided over the ranks, every rank keeps all keys of its heads
+    and writes the output of their query heads -> nothing crosses NVLink."""
 from __future__ import annotations
 
 from typing import NamedTuple, Tuple
@@ -42,6 +44,16 @@ def kv_shard(Sk: int, rank: int, world: int, align: int = 128) -> Tuple[int, int
     per = -(-per // align) * align
     begin = min(rank * per, Sk)
     return begin, min(begin + per, Sk)
+
+
+def head_shard(Hkv: int, G: int, rank: int, world: int):
+    """Decode with the KV heads divided over the ranks (no exchange: the ranks' outputs are disjoint query heads):
+    returns (kv_head_begin, kv_head_end, query_head_begin, query_head_end) of `rank`.  The G query heads of a KV head
+    stay with it; `Hkv` must divide evenly, so that every rank streams the same number of bytes."""
+    if Hkv % world != 0:
+        raise ValueError(f"{Hkv} KV heads do not divide over {world} ranks")
+    lo, hi = unit_range(Hkv, rank, world)
+    return lo, hi, lo * G, hi * G
 
 
 def local_lengths(lengths, begin: int, end: int):
