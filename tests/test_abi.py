@@ -140,3 +140,43 @@ def test_decode_split_suggestion_follows_the_cache_size():
     assert f(32768, 8, 64) == 3           # the ragged batch: eight per SM over 512 groups
     assert f(100, 1, 1) == 1 and f(0, 1, 1) == 1
     assert f(300, 1, 1) == 2              # at least 256 keys per split
+
+
+def test_julia_wrappers_call_only_exported_symbols_with_matching_arity():
+    """Every `ccall((:tylo_b200_x, libtylo), ...)` of the Julia package names a symbol that `include/tylo_b200.h`
+    declares, and passes as many arguments as the declaration has parameters (the Julia sources cannot be executed
+    here, so the binding is checked as text against the header)."""
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    header = (root / "include" / "tylo_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    decl = {}
+    for m in re.finditer(r"\b(tylo_b200_\w+)\s*\(([^;{]*?)\)\s*;", header, flags=re.S):
+        params = m.group(2).strip()
+        decl[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    assert len(decl) > 30
+    seen = 0
+    for jl in (root / "tylo.jl_b200" / "julia" / "Tylo").rglob("*.jl"):
+        text = jl.read_text()
+        for m in re.finditer(r"ccall\(\(:(tylo_b200_\w+), libtylo\),\s*\w+,\s*\(", text):
+            name = m.group(1)
+            assert name in decl, f"{jl.name}: {name} is not declared in the header"
+            # the argument-type tuple follows: count its entries up to the matching parenthesis
+            i, depth, n, nonempty = m.end(), 1, 0, False
+            while depth:
+                c = text[i]
+                if c in "({[":
+                    depth += 1
+                elif c in ")}]":
+                    depth -= 1
+                elif c == "," and depth == 1:
+                    n += 1
+                elif not c.isspace():
+                    nonempty = True
+                i += 1
+            tail = text[m.end():i - 1].rstrip()
+            n_types = 0 if not nonempty else n + (0 if tail.endswith(",") else 1)
+            assert n_types == decl[name], f"{jl.name}: {name} passes {n_types} argument types, the header declares {decl[name]}"
+            seen += 1
+    assert seen >= 20
