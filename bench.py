@@ -305,7 +305,7 @@ def documents(B, S, ndocs, seed):
     return tab, cuts
 
 
-def make_flex(t, torch, seed, bwd=False):
+def make_flex(t, torch, seed, bwd=False, block_list=False):
     import numpy as np
     sy = synth()
     c = C4
@@ -328,7 +328,34 @@ def make_flex(t, torch, seed, bwd=False):
     pairs *= H
     O = torch.empty_like(Q)
     cp = t.allocate_checkpoints_flex_attention(Q, K, V)
-    w = dict(name="flex_bwd" if bwd else "flex_fwd", unit="TFLOP/s", bound="tensor", scale=1e-12)
+    w = dict(name="flex_bwd" if bwd else ("flex_fwd_block_list" if block_list else "flex_fwd"), unit="TFLOP/s", bound="tensor",
+             scale=1e-12)
+    bm = None
+    if block_list:
+        # The same mask as a host-built BlockMask (mods.jl:436-476) of 64 x 64 blocks: a block is listed if any pair in
+        # it survives in any batch entry, full if every pair survives in every batch entry (the list has no batch
+        # axis; the mask mod still runs per pair in listed blocks that are not full).  A query keeps the keys
+        # [lo(q), q] with lo non-decreasing in q, which makes both tests two comparisons per block and batch entry.
+        T = 64
+        nb = S // T
+        los = []
+        for b in range(B):
+            start = np.zeros(S, dtype=np.int64)
+            first = np.r_[0, np.flatnonzero(np.diff(tab[b])) + 1]
+            start[first] = first
+            los.append(np.maximum(np.arange(S) - W, np.maximum.accumulate(start)))
+        cnt = np.zeros(nb, np.int32); idx = np.zeros((nb, nb), np.int32); full = np.zeros((nb, nb), np.int32)
+        for i in range(nb):
+            r0, r1 = i * T, i * T + T - 1
+            for j in range(i + 1):
+                c0, c1 = j * T, j * T + T - 1
+                qs = max(r0, c0)                                   # the first query of the block that may see the block's keys
+                if any(lo[qs] <= c1 for lo in los):
+                    idx[i, cnt[i]] = j
+                    full[i, cnt[i]] = int(r0 >= c1 and all(lo[r1] <= c0 for lo in los))
+                    cnt[i] += 1
+        bm = t.BlockMask(torch.from_numpy(cnt).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(full).cuda(), T, T)
+        w["listed_blocks"] = int(cnt.sum()); w["full_blocks"] = int(full.sum())
 
     def band(b, h, k0):
         """Oracle inputs of the queries [k0, k0 + 1536) of (b, h) with every key they can see."""
@@ -343,7 +370,7 @@ def make_flex(t, torch, seed, bwd=False):
     b0, h0 = B - 1, H - 1
     k0 = min(int(cuts[b0][3]) // 128 * 128, S - 1536)            # a band with a document cut inside
     if not bwd:
-        w.update(step=lambda: t.flex_attention_(O, Q, K, V, score_mod=score, mask_mod=mask, checkpoints=cp),
+        w.update(step=lambda: t.flex_attention_(O, Q, K, V, score_mod=score, mask_mod=mask, checkpoints=cp, block_mask=bm),
                  work=4 * D * pairs, launches=1)
 
         def verify():
@@ -368,8 +395,11 @@ def make_flex(t, torch, seed, bwd=False):
                           parity(Kd.shadow[b0:b0 + 1, h0:h0 + 1, k0:k0 + 512], rK[:, :, ks], what + " [dK]", grad=True),
                           parity(Vd.shadow[b0:b0 + 1, h0:h0 + 1, k0:k0 + 512], rV[:, :, ks], what + " [dV]", grad=True)])
         w["verify"] = verify
-    w["config"] = dict(workload="flex attention %s, bf16: causal & window 1024 & document, softcap 50" % ("backward" if bwd else "forward"),
+    w["config"] = dict(workload="flex attention %s, bf16: causal & window 1024 & document, softcap 50" % ("backward" if bwd else "forward")
+                       + (", walked over a host-built list of 64 x 64 blocks" if block_list else ""),
                        batch=B, seq_len=S, heads=H, head_dim=D, unmasked_pairs=pairs)
+    if block_list:
+        w["config"].update(listed_blocks=w.pop("listed_blocks"), full_blocks=w.pop("full_blocks"))
     return w
 
 
@@ -843,6 +873,7 @@ def main():
         "softmax_bwd": lambda: make_rowwise(t, torch, 1, "softmax_bwd"),
         "mha_fp32": lambda: make_fp32(t, torch, 0),
         "mha_tf32": lambda: make_fp32(t, torch, 0, tf32=True),
+        "flex_fwd_block_list": lambda: make_flex(t, torch, 3, block_list=True),
         "flex_bias_fwd_bwd": lambda: make_variants(t, torch, 5, "bias"),
         "flex_block_list_fwd": lambda: make_variants(t, torch, 6, "block_list"),
     }
