@@ -305,6 +305,32 @@ def documents(B, S, ndocs, seed):
     return tab, cuts
 
 
+def band_block_list(tab, S, W, T):
+    """Host-built block list (mods.jl:436-476) of `causal & window W & document` for the document tables `tab` (B, S):
+    T x T blocks, listed if any pair of the block survives in any batch entry, full if every pair survives in every
+    batch entry.  Returns (count [nb], idx [nb, nb], full [nb, nb]) int32, key blocks in ascending order.  A query
+    keeps the keys [lo(q), q] with lo non-decreasing in q, so both tests are two comparisons per block and entry."""
+    import numpy as np
+    nb = S // T
+    los = []
+    for b in range(tab.shape[0]):
+        start = np.zeros(S, dtype=np.int64)
+        first = np.r_[0, np.flatnonzero(np.diff(tab[b])) + 1]
+        start[first] = first
+        los.append(np.maximum(np.arange(S) - W, np.maximum.accumulate(start)))
+    cnt = np.zeros(nb, np.int32); idx = np.zeros((nb, nb), np.int32); full = np.zeros((nb, nb), np.int32)
+    for i in range(nb):
+        r0, r1 = i * T, i * T + T - 1
+        for j in range(i + 1):
+            c0, c1 = j * T, j * T + T - 1
+            qs = max(r0, c0)                                   # the first query of the block that may see the block's keys
+            if any(lo[qs] <= c1 for lo in los):
+                idx[i, cnt[i]] = j
+                full[i, cnt[i]] = int(r0 >= c1 and all(lo[r1] <= c0 for lo in los))
+                cnt[i] += 1
+    return cnt, idx, full
+
+
 def make_flex(t, torch, seed, bwd=False, block_list=False):
     import numpy as np
     sy = synth()
@@ -337,23 +363,7 @@ def make_flex(t, torch, seed, bwd=False, block_list=False):
         # axis; the mask mod still runs per pair in listed blocks that are not full).  A query keeps the keys
         # [lo(q), q] with lo non-decreasing in q, which makes both tests two comparisons per block and batch entry.
         T = 64
-        nb = S // T
-        los = []
-        for b in range(B):
-            start = np.zeros(S, dtype=np.int64)
-            first = np.r_[0, np.flatnonzero(np.diff(tab[b])) + 1]
-            start[first] = first
-            los.append(np.maximum(np.arange(S) - W, np.maximum.accumulate(start)))
-        cnt = np.zeros(nb, np.int32); idx = np.zeros((nb, nb), np.int32); full = np.zeros((nb, nb), np.int32)
-        for i in range(nb):
-            r0, r1 = i * T, i * T + T - 1
-            for j in range(i + 1):
-                c0, c1 = j * T, j * T + T - 1
-                qs = max(r0, c0)                                   # the first query of the block that may see the block's keys
-                if any(lo[qs] <= c1 for lo in los):
-                    idx[i, cnt[i]] = j
-                    full[i, cnt[i]] = int(r0 >= c1 and all(lo[r1] <= c0 for lo in los))
-                    cnt[i] += 1
+        cnt, idx, full = band_block_list(tab, S, W, T)
         bm = t.BlockMask(torch.from_numpy(cnt).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(full).cuda(), T, T)
         w["listed_blocks"] = int(cnt.sum()); w["full_blocks"] = int(full.sum())
 

@@ -1,4 +1,5 @@
 """CPU: host-side mirror of the Tylo API — mods, host evaluators, descriptors, buffers."""
+import numpy as np
 import pytest
 import torch
 
@@ -176,3 +177,36 @@ def test_tensorcore_keyword_maps_to_the_dtype_code(tylo):
     assert t._fwd_dtype(f32, TFloat32) == t.F32_TF32
     with pytest.raises(ValueError):
         t._fwd_dtype(f32, "fp8")
+
+
+def test_bench_block_list_matches_the_oracle_builder(oracle):
+    """The closed-form block list the bench builds for `causal & window & document` equals the oracle's pairwise
+    builder (mods.jl:436-476) on seeded document tables, and the union / intersection over batch entries."""
+    import importlib.util
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("tylo_bench", Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec); spec.loader.exec_module(bench)
+    rng = np.random.default_rng(1)
+    S, W, T = 384, 150, 64
+    tabs = []
+    for _ in range(2):
+        cuts = np.sort(rng.choice(np.arange(1, S), size=3, replace=False))
+        tabs.append(np.searchsorted(cuts, np.arange(S), side="right").astype(np.int32))
+    keep = lambda tab: (lambda q, kv: bool(q >= kv and q - kv <= W and tab[q] == tab[kv]))
+    for tab in tabs:
+        cnt, idx, full = bench.band_block_list(tab[None], S, W, T)
+        rc, ri, rf = oracle.build_block_mask_ref(keep(tab), S, S, TILE_M=T, TILE_N=T)
+        assert np.array_equal(cnt, rc)
+        for i in range(S // T):
+            assert np.array_equal(idx[i, :cnt[i]], ri[i, :rc[i]]) and np.array_equal(full[i, :cnt[i]], rf[i, :rc[i]])
+    # two batch entries: listed = in either, full = in both
+    cnt, idx, full = bench.band_block_list(np.stack(tabs), S, W, T)
+    any_keep = lambda q, kv: keep(tabs[0])(q, kv) or keep(tabs[1])(q, kv)
+    rc, ri, _ = oracle.build_block_mask_ref(any_keep, S, S, TILE_M=T, TILE_N=T)
+    assert np.array_equal(cnt, rc) and all(np.array_equal(idx[i, :cnt[i]], ri[i, :rc[i]]) for i in range(S // T))
+    singles = [bench.band_block_list(tab[None], S, W, T) for tab in tabs]
+    for i in range(S // T):
+        for n in range(cnt[i]):
+            j = idx[i, n]
+            both = all(any(sj == j and sf for sj, sf in zip(si[i, :sc[i]], sfl[i, :sc[i]])) for sc, si, sfl in singles)
+            assert bool(full[i, n]) == both
