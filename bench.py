@@ -12,10 +12,16 @@ softmax in GB/s, backward and flex in TFLOP/s), each with its own roofline fract
 Multi-GPU (`--gpus N`, launched under torchrun): prefill shards over batch x heads with no
 communication (every rank runs the per-GPU problem: weak scaling); the 1M-token decode extra
 shards the KV sequence across ranks and merges the per-rank (O, max, sum) partials with the
-library's own exchange kernel (peer stores over NVLink into IPC-shared buffers, one launch).
+library's own exchange kernel (peer stores over NVLink into IPC-shared buffers, one launch);
+`decode_1m_heads` cuts the same cache by KV heads instead, which needs no exchange at all.  At N > 1 both decode
+workloads replay eight decode steps per CUDA graph and report the time per decode step beside the replay's.
 
 Strong-scaling prefill (`prefill_fwd_sharded`, `prefill_bwd_sharded`): ONE batch-4 problem whose 32
 (kv-head, batch) units are cut into contiguous ranges, one per rank, no exchange.
+
+Variants outside the contract's configs, each on the tensor-core kernels and each checked against the oracle:
+`mha_tf32` (config 1 with TF32 operands), `flex_bias_fwd_bwd` (bias table with its gradient), `flex_block_list_fwd`
+and `flex_fwd_block_list` (host-built block lists: a causal window, and config 4's own mask).
 
 Inputs come from the package's counter-based generator (`synth.py`: element i of tensor t under seed s
 is the same number on the CPU and on the GPU, however the tensor is sharded).  After a workload has been
