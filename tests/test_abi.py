@@ -83,6 +83,11 @@ def test_flex_descriptor_validation(tylo):
     rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
                                           64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 0, None)
     assert rc == 1
+    # a bias table that is not 16-byte aligned is refused before any launch (the kernels read it with 16-byte loads)
+    md = tylo._MaskDesc(); sd = tylo._ScoreDesc(); sd.flags = tylo.SCORE_BIAS; sd.bias = 0x2004; sd.bias_heads = 1; sd.bias_batch = 1
+    rc = lib.tylo_b200_flex_attention_fwd(f(1), f(2), f(3), f(4), None, None, ctypes.byref(md), ctypes.byref(sd),
+                                          64, 64, 16, 16, 2, 2, 1, 0, 0.0, 1, 1, None)
+    assert rc == 3 and b"16-byte aligned" in lib.tylo_b200_last_error()
 
 
 def test_decode_suggest_splits(tylo):

@@ -77,6 +77,9 @@ static int32_t fill_mods(const char* who, AttnParams& p, const tylo_mask_desc* m
       TYLO_REQUIRE(score->bias_heads > 0 && score->bias_batch > 0, TYLO_ERR_INVALID_ARGUMENT,
                    "%s: BiasScore extents must be positive (heads %d, batch %d)", who, score->bias_heads,
                    score->bias_batch);
+      // the kernels read table rows with 16-byte loads and add to the gradient with 16-byte reductions
+      TYLO_REQUIRE(aligned16(score->bias) && aligned16(score->d_bias), TYLO_ERR_MISALIGNED,
+                   "%s: the bias table and its gradient must be 16-byte aligned", who);
       p.bias = score->bias; p.d_bias = score->d_bias; p.bias_heads = score->bias_heads; p.bias_batch = score->bias_batch;
     }
   }
